@@ -1,4 +1,4 @@
-"""One registry from an architecture's name (config.json `architectures[0]`) to its model.
+"""One registry from an architecture's name (config.json `architectures[0]`, or the string `architecture`) to its model.
 
 The reference picks its safetensors engine by "the path is a folder with *.safetensors"
 (src/main.cpp:169-174, src/app/main_helpers.cpp:464-486) and knows no names.
@@ -26,6 +26,8 @@ class Architecture:
     presets: dict = dataclasses.field(default_factory=dict)
     # single config.json keys a command line may set: (flag, key, type or tuple of choices, help)
     cli_options: tuple = ()
+    # (typed configuration, ModelSpec, weight source) -> ModelSpec: for sizes that only the tensors' shapes give
+    refine_spec: Any = None
 
 
 _ARCHITECTURES: dict[str, Architecture] = {}
@@ -50,9 +52,11 @@ def get_architecture(name: str) -> Architecture:
 
 def architecture_of(raw_config: dict) -> Architecture:
     archs = raw_config.get("architectures")
+    if archs is None and isinstance(raw_config.get("architecture"), str):
+        archs = [raw_config["architecture"]]          # some folders name their one architecture as a string
     if not archs or not isinstance(archs, list):
-        raise ConfigError("config.json: 'architectures' is missing or empty; registered: "
-                          + ", ".join(registered_architectures()))
+        raise ConfigError("config.json: 'architectures' (a list) or 'architecture' (a name) is missing or empty; "
+                          "registered: " + ", ".join(registered_architectures()))
     return get_architecture(archs[0])
 
 

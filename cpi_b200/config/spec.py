@@ -36,11 +36,11 @@ class LayerSpec:
     checkpoint; each part adds its own local names to it.
     """
     prefix: str
-    block: PartSpec          # arrangement, e.g. kind "pre_norm"
-    mixer: PartSpec          # e.g. kind "attention"
-    feed_forward: PartSpec   # e.g. kind "dense_swiglu" or "moe_swiglu"
+    block: PartSpec          # arrangement, e.g. kind "pre_norm" or "hyper_connections"
+    mixer: PartSpec          # e.g. kind "attention", "mamba2", "gla"
+    feed_forward: Optional[PartSpec]   # e.g. kind "dense_swiglu" or "moe_swiglu"; None: the layer has no feed-forward
     mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    feed_forward_norm: Optional[PartSpec]
 
 
 @dataclass(frozen=True)
@@ -65,12 +65,15 @@ class ModelSpec:
     layers: tuple                  # of LayerSpec
     run_order: tuple               # of RunEntry
     final_norm: PartSpec
-    head: PartSpec                 # kind "linear_head", params: weight name (may alias the embedding)
+    head: PartSpec                 # kind "linear_head", params: weight name (may alias the embedding); optional
+                                   # logit_scale (logits * s) and logit_softcap (c * tanh(logits / c) afterwards)
     ignored_tensor_prefixes: tuple = ()
     bos_token_id: Optional[int] = None
     stop_token_ids: tuple = ()
     max_position: int = 0
     initializer_range: float = 0.02
+    residual_streams: int = 1      # copies of the residual that the layers' blocks keep (hyper-connections); all
+                                   # start as the embedding output and the final norm reads their sum
 
     def validate(self) -> None:
         if not self.run_order:

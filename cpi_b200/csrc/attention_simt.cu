@@ -220,6 +220,89 @@ __global__ void __launch_bounds__(256) qkv_post_d128_kernel(QkvPostParams p, int
   }
 }
 
+// The same step in its general form, a block per token: biases, an RMS norm over the whole q projection and the
+// whole k projection (all heads at once, with weights), a rotation of only the first `rot_dims` elements of each
+// head (pairs (i, i + rot_dims / 2); the rest pass), values of another size than keys.  Input rows may be float32
+// while the cache is bfloat16: the row is then rounded once, after the norm and the rotation.
+struct QkvPrepParams {
+  const void* qkv; long qkv_stride;      // [T, NH D + NKV D + NKV DV]
+  const void* bias; int bias_dtype;      // [NH D + NKV D + NKV DV] or null
+  const void* q_norm; const void* k_norm; int norm_dtype; int norm_whole; float norm_eps;     // weights or null
+  const float* inv_freq; int rot_dims;   // [rot_dims / 2] or null
+  void* q_out; void* k_cache; void* v_cache;
+  const int* page_table; int max_blocks; int page_size;
+  const int* token_seq; const int* token_pos; const int* seq_slot;
+  int n_heads, n_kv_heads, head_dim, v_dim, write_kv;
+};
+
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256) qkv_prepare_kernel(QkvPrepParams p) {
+  pdl_launch_dependents();
+  extern __shared__ float row_s[];                       // q then k of this token, float32
+  __shared__ float scratch[32];
+  pdl_wait();
+  const int t = blockIdx.x, tid = threadIdx.x;
+  const int D = p.head_dim, DV = p.v_dim;
+  const int nq = p.n_heads * D, nk = p.write_kv ? p.n_kv_heads * D : 0, nv = p.write_kv ? p.n_kv_heads * DV : 0;
+  const TI* src = reinterpret_cast<const TI*>(p.qkv) + (size_t)t * p.qkv_stride;
+  const int pos = p.token_pos[t];
+  float ssq = 0.f, ssk = 0.f;
+  for (int i = tid; i < nq + nk; i += blockDim.x) {
+    float x = to_f32(src[i]);
+    if (p.bias) x += load_any(p.bias, p.bias_dtype, i);
+    row_s[i] = x;
+    if (i < nq) ssq = fmaf(x, x, ssq); else ssk = fmaf(x, x, ssk);
+  }
+  float inv_q = 1.f, inv_k = 1.f;
+  if (p.norm_whole) {
+    ssq = block_sum(ssq, scratch);
+    inv_q = 1.0f / sqrtf(ssq / (float)nq + p.norm_eps);
+    if (nk) {
+      ssk = block_sum(ssk, scratch);
+      inv_k = 1.0f / sqrtf(ssk / (float)nk + p.norm_eps);
+    }
+  }
+  __syncthreads();
+  size_t kv_row = 0;
+  if (p.write_kv) {
+    const int slot = p.seq_slot[p.token_seq[t]];
+    const int page = p.page_table[(size_t)slot * p.max_blocks + pos / p.page_size];
+    kv_row = (size_t)page * p.n_kv_heads * p.page_size + pos % p.page_size;      // row of kv head 0
+  }
+  const int half = p.rot_dims >> 1;
+  for (int i = tid; i < nq + nk; i += blockDim.x) {
+    const bool is_q = i < nq;
+    const int e = is_q ? i : i - nq;
+    const int hd = e / D, d = e % D;
+    const float inv = is_q ? inv_q : inv_k;
+    const void* nw = is_q ? p.q_norm : p.k_norm;
+    auto normed = [&](int idx, int el) {
+      float x = row_s[idx] * inv;
+      if (p.norm_whole && nw) x *= load_any(nw, p.norm_dtype, el);
+      return x;
+    };
+    float x = normed(i, e);
+    if (p.inv_freq && d < p.rot_dims) {
+      const bool first = d < half;
+      const int f = first ? d : d - half;
+      const float other = first ? normed(i + half, e + half) : normed(i - half, e - half);
+      float sn, cs;
+      sincosf((float)pos * p.inv_freq[f], &sn, &cs);
+      x = first ? x * cs - other * sn : x * cs + other * sn;
+    }
+    if (is_q) {
+      reinterpret_cast<TO*>(p.q_out)[(size_t)t * nq + i] = from_f32<TO>(x);
+    } else {
+      reinterpret_cast<TO*>(p.k_cache)[(kv_row + (size_t)hd * p.page_size) * D + d] = from_f32<TO>(x);
+    }
+  }
+  for (int i = tid; i < nv; i += blockDim.x) {
+    float x = to_f32(src[nq + nk + i]);
+    if (p.bias) x += load_any(p.bias, p.bias_dtype, nq + nk + i);
+    reinterpret_cast<TO*>(p.v_cache)[(kv_row + (size_t)(i / DV) * p.page_size) * DV + i % DV] = from_f32<TO>(x);
+  }
+}
+
 struct AttnParams {
   const void* q; void* out;              // [T, NH D]
   const void* k_cache; const void* v_cache;
@@ -229,6 +312,8 @@ struct AttnParams {
   int window_kind, window_size;          // 0 all keys, 1 chunk of window_size, 2 last window_size keys
   float scale;
   const float* score_bias; int n_dist;   // [NH, n_dist] float32 added to the scaled scores by distance, or null
+  const float* sink;                     // [NH] float32 or null: exp(sink[h]) joins the softmax denominator (no key, no value)
+  int v_dim;                             // elements of a value row (the cache's v stream); keys have head_dim
 };
 
 __device__ __forceinline__ int window_low(int kind, int size, int pos) {
@@ -248,7 +333,7 @@ __global__ void __launch_bounds__(ATT_NT) attention_general_kernel(AttnParams p)
   __shared__ size_t off_s[ATT_NT];
   __shared__ float scratch[32];
   const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
-  const int D = p.head_dim;
+  const int D = p.head_dim, DV = p.v_dim;
   const int kvh = h / (p.n_heads / p.n_kv_heads);
   const int pos = p.token_pos[t];
   const int slot = p.seq_slot[p.token_seq[t]];
@@ -259,7 +344,9 @@ __global__ void __launch_bounds__(ATT_NT) attention_general_kernel(AttnParams p)
   const T* vc = reinterpret_cast<const T*>(p.v_cache);
   const int* table = p.page_table + (size_t)slot * p.max_blocks;
 
+  // a sink is a key without a value whose score is sink[h], unscaled: the running maximum and sum start from it
   float m_run = -INFINITY, l_run = 0.f, acc0 = 0.f, acc1 = 0.f;
+  if (p.sink) { m_run = p.sink[h]; l_run = 1.0f; }
   __syncthreads();
   for (int base = lo; base <= pos; base += ATT_NT) {
     const int kp = base + tid;
@@ -267,9 +354,9 @@ __global__ void __launch_bounds__(ATT_NT) attention_general_kernel(AttnParams p)
     float s = -INFINITY;
     if (valid) {
       const int page = table[kp / p.page_size];
-      const size_t off = (((size_t)page * p.n_kv_heads + kvh) * p.page_size + kp % p.page_size) * D;
-      off_s[tid] = off;
-      const T* kr = kc + off;
+      const size_t row = ((size_t)page * p.n_kv_heads + kvh) * p.page_size + kp % p.page_size;
+      off_s[tid] = row;
+      const T* kr = kc + row * D;
       float dot = 0.f;
       for (int d = 0; d < D; ++d) dot = fmaf(q_s[d], to_f32(kr[d]), dot);
       s = dot * p.scale;
@@ -283,19 +370,19 @@ __global__ void __launch_bounds__(ATT_NT) attention_general_kernel(AttnParams p)
     const int nv = min(ATT_NT, pos - base + 1);
     acc0 *= alpha; acc1 *= alpha;
     for (int j = 0; j < nv; ++j) {
-      const T* vr = vc + off_s[j];
+      const T* vr = vc + off_s[j] * DV;
       const float pj = p_s[j];
-      if (tid < D) acc0 = fmaf(pj, to_f32(vr[tid]), acc0);
-      if (tid + ATT_NT < D) acc1 = fmaf(pj, to_f32(vr[tid + ATT_NT]), acc1);
+      if (tid < DV) acc0 = fmaf(pj, to_f32(vr[tid]), acc0);
+      if (tid + ATT_NT < DV) acc1 = fmaf(pj, to_f32(vr[tid + ATT_NT]), acc1);
     }
     l_run = l_run * alpha + l_tile;
     m_run = m_new;
     __syncthreads();
   }
   const float inv = 1.0f / fmaxf(l_run, 1e-20f);
-  T* o = reinterpret_cast<T*>(p.out) + ((size_t)t * p.n_heads + h) * D;
-  if (tid < D) o[tid] = from_f32<T>(acc0 * inv);
-  if (tid + ATT_NT < D) o[tid + ATT_NT] = from_f32<T>(acc1 * inv);
+  T* o = reinterpret_cast<T*>(p.out) + ((size_t)t * p.n_heads + h) * DV;
+  if (tid < DV) o[tid] = from_f32<T>(acc0 * inv);
+  if (tid + ATT_NT < DV) o[tid + ATT_NT] = from_f32<T>(acc1 * inv);
 }
 
 }  // namespace cpi
@@ -342,19 +429,54 @@ extern "C" int cpi_qkv_post(const void* qkv, long qkv_stride, void* q_out, void*
   return check_launch("qkv_post");
 }
 
+extern "C" int cpi_qkv_prepare(const void* qkv, int in_dtype, long qkv_stride, const void* bias, int bias_dtype,
+                               const void* q_norm, const void* k_norm, int norm_dtype, int norm_whole, float norm_eps,
+                               const float* inv_freq, int rot_dims, void* q_out, void* k_cache, void* v_cache,
+                               int out_dtype, const int* page_table, int max_blocks, int page_size,
+                               const int* token_seq, const int* token_pos, const int* seq_slot, int n_tokens,
+                               int n_heads, int n_kv_heads, int head_dim, int v_dim, int write_kv,
+                               cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  CPI_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0,
+              "qkv_prepare: %d heads cannot be grouped over %d key/value heads", n_heads, n_kv_heads);
+  CPI_REQUIRE(head_dim >= 1 && v_dim >= 1, "qkv_prepare: bad head sizes %d / %d", head_dim, v_dim);
+  CPI_REQUIRE(inv_freq == nullptr || (rot_dims >= 2 && rot_dims % 2 == 0 && rot_dims <= head_dim),
+              "qkv_prepare: %d rotated elements of a head of %d (an even number up to the head size)", rot_dims, head_dim);
+  QkvPrepParams p{qkv, qkv_stride, bias, bias_dtype, q_norm, k_norm, norm_dtype, norm_whole, norm_eps, inv_freq,
+                  rot_dims, q_out, k_cache, v_cache, page_table, max_blocks, page_size, token_seq, token_pos,
+                  seq_slot, n_heads, n_kv_heads, head_dim, v_dim, write_kv};
+  const size_t smem = (size_t)(n_heads + (write_kv ? n_kv_heads : 0)) * head_dim * sizeof(float);
+  CPI_REQUIRE(smem <= 200 * 1024, "qkv_prepare: a q and k row of %zu bytes does not fit in shared memory", smem);
+#define CPI_PREP(TI, TO)                                                                                       \
+  do {                                                                                                         \
+    auto kern = qkv_prepare_kernel<TI, TO>;                                                                    \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
+    cpi::launch_pdl(kern, dim3(n_tokens), dim3(256), smem, stream, p);                                         \
+  } while (0)
+  if (in_dtype == kF32 && out_dtype == kF32) CPI_PREP(float, float);
+  else if (in_dtype == kF32 && out_dtype == kBF16) CPI_PREP(float, __nv_bfloat16);
+  else if (in_dtype == kBF16 && out_dtype == kBF16) CPI_PREP(__nv_bfloat16, __nv_bfloat16);
+  else { set_error("qkv_prepare: input dtype %d with cache dtype %d is not supported", in_dtype, out_dtype); return 1; }
+#undef CPI_PREP
+  return check_launch("qkv_prepare");
+}
+
 extern "C" int cpi_attention_general(const void* q, void* out, const void* k_cache, const void* v_cache,
                                      int dtype, const int* page_table, int max_blocks, int page_size,
                                      const int* token_seq, const int* token_pos, const int* seq_slot,
                                      int n_tokens, int n_heads, int n_kv_heads, int head_dim,
                                      int window_kind, int window_size, float scale, const float* score_bias,
-                                     int n_dist, cudaStream_t stream) {
+                                     int n_dist, const float* sink, int v_dim, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
-  if (check_head("attention", n_heads, n_kv_heads, head_dim)) return 1;
+  CPI_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0,
+              "attention: %d heads cannot be grouped over %d key/value heads", n_heads, n_kv_heads);
+  CPI_REQUIRE(head_dim >= 1 && head_dim <= 256 && v_dim >= 1 && v_dim <= 256,
+              "attention: head sizes %d (keys) and %d (values) are not supported (1 to 256)", head_dim, v_dim);
   CPI_REQUIRE(score_bias == nullptr || n_dist > 0, "attention: a score bias table needs at least one distance");
   CPI_REQUIRE(window_kind == 0 || window_size > 0, "attention: window kind %d needs a size > 0", window_kind);
   CPI_REQUIRE(n_heads <= 65535, "attention: too many heads (%d)", n_heads);
   AttnParams p{q, out, k_cache, v_cache, page_table, max_blocks, page_size, token_seq, token_pos, seq_slot,
-               n_heads, n_kv_heads, head_dim, window_kind, window_size, scale, score_bias, n_dist};
+               n_heads, n_kv_heads, head_dim, window_kind, window_size, scale, score_bias, n_dist, sink, v_dim};
   dim3 grid(n_tokens, n_heads);
   CPI_DISPATCH_DTYPE(dtype, T, cpi::launch_pdl(attention_general_kernel<T>, grid, ATT_NT, 0, stream, p));
   return check_launch("attention_general");

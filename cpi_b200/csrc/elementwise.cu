@@ -44,7 +44,7 @@ __global__ void embedding_kernel(const int* __restrict__ tokens, const TT* __res
 template <typename TX, typename TO>
 __global__ void rmsnorm_kernel(const TX* __restrict__ x, long x_stride, const int* __restrict__ rows,
                                const void* __restrict__ w, int w_dtype, TO* __restrict__ out,
-                               long out_stride, int n, float eps) {
+                               long out_stride, int n, float eps, float w_offset) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float scratch[32];
@@ -69,7 +69,7 @@ __global__ void rmsnorm_kernel(const TX* __restrict__ x, long x_stride, const in
       const int i = threadIdx.x + j * blockDim.x;
       if (i < n) {
         float y = v[j] * inv;
-        if (w) y *= load_any(w, w_dtype, i);
+        if (w) y *= w_offset + load_any(w, w_dtype, i);
         o[i] = from_f32<TO>(y);
       }
     }
@@ -84,7 +84,7 @@ __global__ void rmsnorm_kernel(const TX* __restrict__ x, long x_stride, const in
   const float inv = 1.0f / sqrtf(ss / (float)n + eps);
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
     float v = to_f32(xr[i]) * inv;
-    if (w) v *= load_any(w, w_dtype, i);
+    if (w) v *= w_offset + load_any(w, w_dtype, i);
     o[i] = from_f32<TO>(v);
   }
 }
@@ -96,7 +96,7 @@ template <typename TO>
 __global__ void __launch_bounds__(256) rmsnorm_vec4_kernel(const float* __restrict__ x, long x_stride,
                                                            const int* __restrict__ rows, const void* __restrict__ w,
                                                            int w_dtype, TO* __restrict__ out, long out_stride, int n,
-                                                           float eps) {
+                                                           float eps, float w_offset) {
   pdl_launch_dependents();
   __shared__ float scratch[32];
   constexpr int PER = 8;
@@ -115,6 +115,7 @@ __global__ void __launch_bounds__(256) rmsnorm_vec4_kernel(const float* __restri
         const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
         g[j] = make_float4(lo.x, lo.y, hi.x, hi.y);
       }
+      g[j].x += w_offset; g[j].y += w_offset; g[j].z += w_offset; g[j].w += w_offset;
     }
   }
   pdl_wait();
@@ -198,15 +199,32 @@ __global__ void moe_combine_vec4_kernel(float* __restrict__ residual, const TY* 
   *reinterpret_cast<float4*>(res) = acc;
 }
 
-template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter) {
+// act(gate) * up over rows [gate | up]; act: 0 silu, 1 the tanh form of gelu
+// 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))).
+__device__ __forceinline__ float gate_act(float a, int act) {
+  if (act == 1) return 0.5f * a * (1.0f + tanhf(0.7978845608028654f * (a + 0.044715f * a * a * a)));
+  return a / (1.0f + expf(-a));
+}
+
+template <typename TI, typename T>
+__global__ void swiglu_kernel(const TI* __restrict__ gu, T* __restrict__ out, int inter, int act) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
-  const T* g = gu + (size_t)t * 2 * inter;
+  const TI* g = gu + (size_t)t * 2 * inter;
   for (int i = threadIdx.x; i < inter; i += blockDim.x) {
     const float a = to_f32(g[i]), b = to_f32(g[inter + i]);
-    out[(size_t)t * inter + i] = from_f32<T>(a / (1.0f + expf(-a)) * b);
+    out[(size_t)t * inter + i] = from_f32<T>(gate_act(a, act) * b);
+  }
+}
+
+// logits <- cap * tanh(logits * scale / cap), or logits * scale when cap is 0.
+__global__ void logit_post_kernel(float* __restrict__ logits, long n, float scale, float cap) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+    const float v = logits[i] * scale;
+    logits[i] = cap > 0.f ? cap * tanhf(v / cap) : v;
   }
 }
 
@@ -244,7 +262,7 @@ extern "C" int cpi_embedding(const int* tokens, const void* table, int table_dty
 
 extern "C" int cpi_rmsnorm(const void* x, int x_dtype, long x_stride, const int* rows, const void* w,
                            int w_dtype, void* out, int out_dtype, long out_stride, int n_rows, int n,
-                           float eps, cudaStream_t stream) {
+                           float eps, float w_offset, cudaStream_t stream) {
   if (n_rows == 0) return 0;
   CPI_REQUIRE(n_rows > 0 && n > 0, "rmsnorm: bad sizes rows=%d n=%d", n_rows, n);
   const int out_esz = out_dtype == kF32 ? 4 : 2;
@@ -252,13 +270,13 @@ extern "C" int cpi_rmsnorm(const void* x, int x_dtype, long x_stride, const int*
       (reinterpret_cast<uintptr_t>(w) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 && (out_stride * out_esz) % 16 == 0) {
     CPI_DISPATCH_DTYPE(out_dtype, TO,
         (cpi::launch_pdl(rmsnorm_vec4_kernel<TO>, n_rows, 256, 0, stream, (const float*)x, x_stride, rows, w, w_dtype,
-                         (TO*)out, out_stride, n, eps)));
+                         (TO*)out, out_stride, n, eps, w_offset)));
     return check_launch("rmsnorm");
   }
   const int threads = n <= 256 ? 64 : (n <= 2048 ? 256 : 512);
   CPI_DISPATCH_DTYPE(x_dtype, TX, CPI_DISPATCH_DTYPE(out_dtype, TO,
       (cpi::launch_pdl(rmsnorm_kernel<TX, TO>, n_rows, threads, 0, stream, (const TX*)x, x_stride, rows, w, w_dtype,
-                                                              (TO*)out, out_stride, n, eps))));
+                                                              (TO*)out, out_stride, n, eps, w_offset))));
   return check_launch("rmsnorm");
 }
 
@@ -282,6 +300,27 @@ extern "C" int cpi_moe_combine(float* residual, const void* y, int y_dtype, cons
 
 extern "C" int cpi_swiglu(const void* gate_up, void* out, int dtype, int n_rows, int inter, cudaStream_t stream) {
   if (n_rows == 0) return 0;
-  CPI_DISPATCH_DTYPE(dtype, T, cpi::launch_pdl(swiglu_kernel<T>, n_rows, 256, 0, stream, (const T*)gate_up, (T*)out, inter));
+  CPI_DISPATCH_DTYPE(dtype, T, cpi::launch_pdl(swiglu_kernel<T, T>, n_rows, 256, 0, stream, (const T*)gate_up, (T*)out, inter, 0));
   return check_launch("swiglu");
+}
+
+// out = act(gate) * up for rows [gate | up] of float32 or of out's dtype; act 0 = silu, 1 = gelu (tanh form)
+extern "C" int cpi_gated_act(const void* gate_up, int in_dtype, void* out, int out_dtype, int n_rows, int inter,
+                             int act, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  CPI_REQUIRE(act == 0 || act == 1, "gated_act: unknown activation %d", act);
+  if (in_dtype == kF32) {
+    CPI_DISPATCH_DTYPE(out_dtype, T, cpi::launch_pdl(swiglu_kernel<float, T>, n_rows, 256, 0, stream, (const float*)gate_up, (T*)out, inter, act));
+  } else {
+    CPI_REQUIRE(in_dtype == out_dtype, "gated_act: bfloat16 rows give bfloat16 rows");
+    cpi::launch_pdl(swiglu_kernel<__nv_bfloat16, __nv_bfloat16>, n_rows, 256, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, act);
+  }
+  return check_launch("gated_act");
+}
+
+extern "C" int cpi_logit_post(float* logits, long n, float scale, float cap, cudaStream_t stream) {
+  if (n == 0) return 0;
+  const int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
+  cpi::launch_pdl(logit_post_kernel, blocks, 256, 0, stream, logits, n, scale, cap);
+  return check_launch("logit_post");
 }

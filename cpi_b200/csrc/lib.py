@@ -19,7 +19,7 @@ WINDOW_KINDS = {"full": WINDOW_FULL, "chunk": WINDOW_CHUNK, "sliding": WINDOW_SL
 MAX_DECODE_SPLITS = 256          # key splits that the combine kernel of decode attention takes
 PREFILL_TILE_ROWS = 256          # most query rows of one sequence that a block of the prefill attention kernel takes
 
-ABI_VERSION = 1                  # what cpi_abi_version() of a matching library answers
+ABI_VERSION = 2                  # what cpi_abi_version() of a matching library answers
 
 _lib = None
 scratch_generation = 0    # grows whenever a scratch buffer of this module is (re)allocated
@@ -98,8 +98,8 @@ def embedding(tokens, table, out, err_flag):
           c_int(table.shape[0]), _p(err_flag), _stream())
 
 
-def rmsnorm(x, weight, eps, out, rows=None):
-    """out[r] = x[rows[r] or r] * rsqrt(mean(x^2) + eps) * weight; weight may be None."""
+def rmsnorm(x, weight, eps, out, rows=None, weight_offset=0.0):
+    """out[r] = x[rows[r] or r] * rsqrt(mean(x^2) + eps) * (weight_offset + weight); weight may be None."""
     _need_cuda(x, weight, out, rows)
     _rowmajor(x, "rmsnorm x"); _rowmajor(out, "rmsnorm out")
     n_rows, n = out.shape
@@ -108,7 +108,7 @@ def rmsnorm(x, weight, eps, out, rows=None):
     assert weight is None or (weight.numel() == n and weight.is_contiguous())
     _call("cpi_rmsnorm", _p(x), c_int(dtype_code(x.dtype)), c_long(x.stride(0)), _p(rows), _p(weight),
           c_int(F32 if weight is None else dtype_code(weight.dtype)), _p(out), c_int(dtype_code(out.dtype)),
-          c_long(out.stride(0)), c_int(n_rows), c_int(n), c_float(eps), _stream())
+          c_long(out.stride(0)), c_int(n_rows), c_int(n), c_float(eps), c_float(weight_offset), _stream())
 
 
 def gemm_simt(a, w, out, mode=MODE_STORE, *, n_out=None, m_rows=None, a_rows=None, out_rows=None,
@@ -320,19 +320,145 @@ def qkv_post(qkv, q_out, k_cache, v_cache, page_table, page_size, token_seq, tok
 
 
 def attention_general(q, out, k_cache, v_cache, page_table, page_size, token_seq, token_pos, seq_slot, *,
-                      n_heads, n_kv_heads, head_dim, window_kind, window_size, scale, score_bias=None):
+                      n_heads, n_kv_heads, head_dim, window_kind, window_size, scale, score_bias=None, sink=None,
+                      value_dim=None):
     """Attention of any head size and dtype over the paged cache.  `score_bias`: float32 [heads, n_dist] added
-    to the scaled scores, indexed by the distance query position - key position (the last column for longer)."""
-    _need_cuda(q, out, k_cache, v_cache, page_table, token_seq, token_pos, seq_slot, score_bias)
-    assert q.is_contiguous() and out.is_contiguous() and q.dtype == out.dtype == k_cache.dtype
+    to the scaled scores, indexed by the distance query position - key position (the last column for longer).
+    `sink`: float32 [heads]; exp(sink[h]) is one more term of the softmax denominator, without a key or a value.
+    `value_dim`: elements of a value row when it differs from the keys' `head_dim`."""
+    _need_cuda(q, out, k_cache, v_cache, page_table, token_seq, token_pos, seq_slot, score_bias, sink)
+    assert q.is_contiguous() and out.is_contiguous() and q.dtype == out.dtype == k_cache.dtype == v_cache.dtype
     assert score_bias is None or (score_bias.dtype == torch.float32 and score_bias.is_contiguous()
                                   and score_bias.dim() == 2 and score_bias.shape[0] == n_heads)
+    assert sink is None or (sink.dtype == torch.float32 and sink.is_contiguous() and sink.numel() == n_heads)
+    value_dim = head_dim if value_dim is None else int(value_dim)
+    assert k_cache.shape[-1] == head_dim and v_cache.shape[-1] == value_dim and out.shape[-1] == n_heads * value_dim
     T = q.shape[0]
     _call("cpi_attention_general", _p(q), _p(out), _p(k_cache), _p(v_cache), c_int(dtype_code(q.dtype)),
           _p(page_table), c_int(page_table.shape[1]), c_int(page_size), _p(token_seq), _p(token_pos),
           _p(seq_slot), c_int(T), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_int(window_kind),
           c_int(window_size), c_float(scale), _p(score_bias),
-          c_int(0 if score_bias is None else score_bias.shape[1]), _stream())
+          c_int(0 if score_bias is None else score_bias.shape[1]), _p(sink), c_int(value_dim), _stream())
+
+
+def qkv_prepare(qkv, q_out, k_cache, v_cache, page_table, page_size, token_seq, token_pos, seq_slot, *, n_heads,
+                n_kv_heads, head_dim, value_dim, bias=None, q_norm=None, k_norm=None, norm_whole=False, norm_eps=0.0,
+                inv_freq=None, rotary_dims=0, write_kv=True):
+    """The general form of `qkv_post`, a block per token: rows [q | k | v] (float32 or the cache's dtype) get
+    their bias, q and k an RMS norm over the whole projection (`norm_whole`, weights `q_norm` / `k_norm`), the
+    first `rotary_dims` elements of each head their rotation; q goes to q_out, k and v into the cache pages."""
+    _need_cuda(qkv, q_out, k_cache, v_cache, page_table, token_seq, token_pos, seq_slot, bias, q_norm, k_norm, inv_freq)
+    _rowmajor(qkv, "qkv_prepare qkv")
+    T = qkv.shape[0]
+    assert q_out.is_contiguous() and q_out.shape[1] == n_heads * head_dim
+    assert k_cache is None or (k_cache.dtype == q_out.dtype == v_cache.dtype and k_cache.shape[-1] == head_dim
+                               and v_cache.shape[-1] == value_dim)
+    assert inv_freq is None or (inv_freq.dtype == torch.float32 and inv_freq.numel() == rotary_dims // 2)
+    assert bias is None or bias.is_contiguous()
+    nw = q_norm if q_norm is not None else k_norm
+    assert q_norm is None or k_norm is None or q_norm.dtype == k_norm.dtype
+    _call("cpi_qkv_prepare", _p(qkv), c_int(dtype_code(qkv.dtype)), c_long(qkv.stride(0)), _p(bias),
+          c_int(F32 if bias is None else dtype_code(bias.dtype)), _p(q_norm), _p(k_norm),
+          c_int(F32 if nw is None else dtype_code(nw.dtype)), c_int(int(norm_whole)), c_float(norm_eps),
+          _p(inv_freq), c_int(rotary_dims), _p(q_out), _p(k_cache), _p(v_cache), c_int(dtype_code(q_out.dtype)),
+          _p(page_table), c_int(page_table.shape[1]), c_int(page_size), _p(token_seq), _p(token_pos), _p(seq_slot),
+          c_int(T), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_int(value_dim), c_int(int(write_kv)),
+          _stream())
+
+
+def hc_step(x, *, y=None, mix=None, write=None, read=None, rows=None, norm_weight=None, norm_offset=0.0, eps=0.0,
+            h_out=None, sum_out=None):
+    """One boundary of a residual kept as streams x [S, T, W] (float32): with `y` [T, W] the write-back
+    x_t <- sum_s mix[s, t] x_s + write[t] y; with `h_out` the next read u = sum_s read[s] x_s (read None: ones),
+    normalised to h_out = u * rsqrt(mean(u^2) + eps) * (norm_offset + norm_weight); `rows` picks tokens (without
+    y only); `sum_out` also receives u."""
+    _need_cuda(x, y, mix, write, read, rows, norm_weight, h_out, sum_out)
+    assert x.dim() == 3 and x.dtype == torch.float32 and x.stride(2) == 1 and x.stride(1) == x.shape[2]
+    S, T, W = x.shape
+    n = T if rows is None else rows.numel()
+    for c in (mix, write, read):
+        assert c is None or (c.dtype == torch.float32 and c.is_contiguous())
+    assert y is None or (y.dtype == torch.float32 and y.shape == (T, W) and y.stride(1) == 1)
+    assert h_out is None or (h_out.shape == (n, W) and h_out.stride(1) == 1)
+    assert sum_out is None or (sum_out.dtype == torch.float32 and sum_out.is_contiguous() and sum_out.shape == (n, W))
+    assert rows is None or rows.dtype == torch.int32
+    _call("cpi_hc_step", _p(x), c_long(x.stride(0)), c_int(S), c_int(n), c_int(W), _p(y),
+          c_long(0 if y is None else y.stride(0)), _p(mix), _p(write), _p(read), _p(rows), _p(norm_weight),
+          c_int(F32 if norm_weight is None else dtype_code(norm_weight.dtype)), c_float(norm_offset), c_float(eps),
+          _p(h_out), c_int(F32 if h_out is None else dtype_code(h_out.dtype)),
+          c_long(0 if h_out is None else h_out.stride(0)), _p(sum_out), _stream())
+
+
+def causal_conv(x, weight, bias, carry, out, batch, *, silu=True):
+    """out[t, c] = act(bias[c] + sum_j weight[c, j] x[t - (taps - 1) + j, c]) per sequence of the step; inputs
+    before the step's first token come from carry[slot] ([slots, taps - 1, C] float32), which afterwards holds the
+    sequence's last taps - 1 inputs.  x, out: float32 [T, C] (x may be a column slice)."""
+    _need_cuda(x, weight, bias, carry, out)
+    T, C = x.shape
+    taps = weight.shape[1]
+    assert x.dtype == torch.float32 and out.dtype == torch.float32 and x.stride(1) == 1 and out.stride(1) == 1
+    assert weight.is_contiguous() and weight.shape[0] == C and (bias is None or (bias.dtype == weight.dtype and bias.numel() == C))
+    assert carry.dtype == torch.float32 and carry.is_contiguous() and tuple(carry.shape[1:]) == (max(taps - 1, 0), C)
+    _call("cpi_causal_conv", _p(x), c_long(x.stride(0)), _p(weight), _p(bias), c_int(dtype_code(weight.dtype)),
+          _p(carry), _p(batch.token_seq), _p(batch.token_pos), _p(batch.seq_slot), _p(batch.seq_start),
+          _p(batch.seq_tok0), _p(batch.seq_new), _p(out), c_long(out.stride(0)), c_int(T), c_int(batch.n_seqs),
+          c_int(C), c_int(taps), c_int(int(silu)), _stream())
+    global launch_count
+    launch_count += int(taps > 1)
+
+
+def linear_scan(k, q, v, state, out, batch, *, n_heads, heads_per_group, n_rows, n_cols, z=None, z_bias=None,
+                tau=1.0, dt=None, dt_bias=None, a_log=None, skip=None, q_scale=1.0):
+    """The recurrence S_t = diag(a_t) S_{t-1} + k_t v_t^T, o_t = S_t^T q_t (+ skip v_t) per sequence and head over the
+    state [slots, heads, n_rows, n_cols] (float32, updated in place).  Give `z` [T, heads * n_rows] for a decay per
+    row, a = sigmoid(z + z_bias)^(1 / tau); or `dt` [T, heads] for a decay per head with a step size,
+    dt' = softplus(dt + dt_bias), a = exp(-exp(a_log) dt'), v' = dt' v.  All rows float32 (column slices allowed)."""
+    small = [t for t in (z_bias, dt_bias, a_log, skip) if t is not None]
+    _need_cuda(k, q, v, state, out, z, dt, *small)
+    for t in (k, q, v, out, z, dt):
+        assert t is None or (t.dtype == torch.float32 and t.dim() == 2 and t.stride(1) == 1)
+    assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (n_heads, n_rows, n_cols)
+    sd = small[0].dtype if small else torch.float32
+    assert all(t.dtype == sd and t.is_contiguous() for t in small)
+    _call("cpi_linear_scan", _p(k), c_long(k.stride(0)), _p(q), c_long(q.stride(0)), _p(v), c_long(v.stride(0)),
+          _p(z), c_long(0 if z is None else z.stride(0)), _p(z_bias), c_float(1.0 / float(tau)),
+          _p(dt), c_long(0 if dt is None else dt.stride(0)), _p(dt_bias), _p(a_log), _p(skip), c_int(dtype_code(sd)),
+          c_float(q_scale), _p(state), _p(out), c_long(out.stride(0)), _p(batch.seq_slot), _p(batch.seq_tok0),
+          _p(batch.seq_new), c_int(batch.n_seqs), c_int(n_heads), c_int(heads_per_group), c_int(n_rows), c_int(n_cols),
+          _stream())
+
+
+def gated_norm(y, gate, weight, out, *, parts, gate_first, eps):
+    """out = norm(y * silu(gate)) * weight (gate_first) or norm(y) * weight * silu(gate): an RMS norm over each of
+    `parts` equal pieces of a row by its own mean square; weight index = element % len(weight).  y, gate float32."""
+    _need_cuda(y, gate, weight, out)
+    T, W = y.shape
+    assert y.dtype == torch.float32 and y.stride(1) == 1 and out.stride(1) == 1 and out.shape == (T, W)
+    assert gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape == (T, W))
+    assert weight is None or weight.is_contiguous()
+    _call("cpi_gated_norm", _p(y), c_long(y.stride(0)), _p(gate), c_long(0 if gate is None else gate.stride(0)),
+          _p(weight), c_int(F32 if weight is None else dtype_code(weight.dtype)),
+          c_int(0 if weight is None else weight.numel()), _p(out), c_int(dtype_code(out.dtype)), c_long(out.stride(0)),
+          c_int(T), c_int(W), c_int(parts), c_int(int(gate_first)), c_float(eps), _stream())
+
+
+GATE_ACTS = {"silu": 0, "gelu_tanh": 1}
+
+
+def gated_act(gate_up, out, act: str):
+    """out = act(gate) * up for rows [gate | up] (float32, or out's dtype)."""
+    _need_cuda(gate_up, out)
+    T, I = out.shape
+    assert gate_up.shape == (T, 2 * I) and gate_up.is_contiguous() and out.is_contiguous()
+    _call("cpi_gated_act", _p(gate_up), c_int(dtype_code(gate_up.dtype)), _p(out), c_int(dtype_code(out.dtype)),
+          c_int(T), c_int(I), c_int(GATE_ACTS[act]), _stream())
+
+
+def logit_post(logits, scale: float, softcap: float):
+    """logits <- softcap * tanh(logits * scale / softcap) in place (softcap 0: only the scale)."""
+    _need_cuda(logits)
+    assert logits.dtype == torch.float32 and logits.is_contiguous()
+    _call("cpi_logit_post", _p(logits), c_long(logits.numel()), c_float(scale), c_float(softcap), _stream())
 
 
 _dec_scratch = {}

@@ -1,0 +1,332 @@
+// Recurrent mixers: a short causal convolution with carried inputs, a linear recurrence over a matrix state
+// per head, and the gated norm that follows it.
+//
+//   causal_conv        out[t, c] = act(bias[c] + sum_j w[c, j] * in[t - (taps - 1) + j, c]); inputs before a
+//                      step's first token come from the sequence's carried inputs (the last taps - 1 of the
+//                      steps before, zeros at the start of the sequence).
+//   conv_carry         after the convolution: the carried inputs become the last taps - 1 inputs seen so far.
+//   linear_scan        per sequence and head, a state S [N rows, Dv columns] in float32 that lives in a slot:
+//                        S_t = diag(a_t) S_{t-1} + k_t v_t^T,   o_t = S_t^T q_t (+ skip * v_t)
+//                      in two flavours: a decay per row, a_t = sigmoid(z_t + bias)^(1 / tau) (gated linear
+//                      attention; q scaled by a constant), or one decay per head with a step size,
+//                      dt = softplus(raw_t + dt_bias), a_t = exp(-exp(A_log) dt), v_t' = dt v_t (the selective
+//                      state-space form, where k is called B, q is called C and heads share B and C in groups).
+//                      Decays, step sizes and the state are float32 whatever the activations are.
+//   gated_norm         out = norm_g(y * silu(g)) * w  or  norm_g(y) * w * silu(g): an RMS norm over equal parts
+//                      of a row (each part by its own mean square), gate before or after.
+//
+// A sequence's tokens are visited in order by one block per (sequence, head, slice of columns) with the same
+// arithmetic whether they come in one step or one at a time, so results do not depend on how a prompt is cut.
+#include "common.cuh"
+
+namespace cpi {
+
+constexpr int CONV_MAX_TAPS = 8;
+
+struct ConvParams {
+  const float* in; long in_stride;       // [T, C] (a column slice of a wider row)
+  const void* w; const void* bias; int w_dtype;      // [C, taps], [C] or null
+  float* carry;                          // [slots, taps - 1, C] float32
+  const int* token_seq; const int* token_pos; const int* seq_slot; const int* seq_start;
+  const int* seq_tok0; const int* seq_new;
+  float* out; long out_stride;           // [T, C] float32
+  int channels, taps, silu;
+};
+
+__device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
+
+__global__ void __launch_bounds__(256) causal_conv_kernel(ConvParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= p.channels) return;
+  const int s = p.token_seq[t];
+  const int local = p.token_pos[t] - p.seq_start[s];          // tokens of this sequence before t in this step
+  const float* carry = p.carry + (size_t)p.seq_slot[s] * (p.taps - 1) * p.channels;
+  float acc = p.bias ? load_any(p.bias, p.w_dtype, c) : 0.f;
+  for (int j = 0; j < p.taps; ++j) {
+    const int back = p.taps - 1 - j;                          // how many tokens before t
+    float x;
+    if (back <= local) x = p.in[(size_t)(t - back) * p.in_stride + c];
+    else x = carry[(size_t)(p.taps - 1 - (back - local)) * p.channels + c];
+    acc = fmaf(load_any(p.w, p.w_dtype, (size_t)c * p.taps + j), x, acc);
+  }
+  p.out[(size_t)t * p.out_stride + c] = p.silu ? silu_f(acc) : acc;
+}
+
+__global__ void __launch_bounds__(256) conv_carry_kernel(ConvParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int s = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= p.channels) return;
+  const int n = p.seq_new[s], tok0 = p.seq_tok0[s], keep = p.taps - 1;
+  float* carry = p.carry + (size_t)p.seq_slot[s] * keep * p.channels;
+  float v[CONV_MAX_TAPS];
+#pragma unroll
+  for (int j = 0; j < CONV_MAX_TAPS; ++j) {
+    if (j < keep) {
+      const int idx = n - keep + j;                           // index among this step's tokens; negative: an older input
+      v[j] = idx >= 0 ? p.in[(size_t)(tok0 + idx) * p.in_stride + c] : carry[(size_t)(j + n) * p.channels + c];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < CONV_MAX_TAPS; ++j)
+    if (j < keep) carry[(size_t)j * p.channels + c] = v[j];
+}
+
+// ---- the recurrence ---------------------------------------------------------------------------------------
+struct ScanParams {
+  const float* k; long k_stride;         // [T, groups * N]
+  const float* q; long q_stride;         // [T, groups * N]
+  const float* v; long v_stride;         // [T, H * Dv]
+  const float* z; long z_stride;         // row decays before the sigmoid [T, H * N]      (row flavour)
+  const void* z_bias; float inv_tau;     // [H * N] or null
+  const float* dt; long dt_stride;       // raw step sizes [T, H]                         (head flavour)
+  const void* dt_bias; const void* a_log; const void* skip;      // [H] each; skip may be null
+  int small_dtype;                       // dtype of z_bias, dt_bias, a_log, skip
+  float q_scale;
+  float* state;                          // [slots, H, N, Dv]
+  float* out; long out_stride;           // [T, H * Dv]
+  const int* seq_slot; const int* seq_tok0; const int* seq_new;
+  int n_heads, heads_per_group, n_rows, n_cols;      // H, H / groups, N, Dv
+  int chunk;                             // tokens staged in shared memory at a time
+};
+
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
+__device__ __forceinline__ float log_sigmoid_f(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
+
+// Threads of a warp: lane = kk * PVW + pp with KS lanes (kk) sharing a column and PVW = 32 / KS columns (pp) per
+// warp.  Lane kk owns the state rows kk * NPT .. kk * NPT + NPT - 1 of its column in registers.  A chunk of
+// tokens is staged in shared memory: per token the rows' k, q and decay, each lane group's NPT values followed
+// by four words of padding, so that the 16-byte reads of different kk fall into different banks.
+template <int NPT, int KS, bool ROW_DECAY>
+__global__ void __launch_bounds__(128) linear_scan_kernel(ScanParams p) {
+  pdl_launch_dependents();
+  extern __shared__ __align__(16) float smem[];
+  constexpr int PVW = 32 / KS, ROWP = KS * (NPT + 4);
+  const int nwarps = blockDim.x >> 5, pvb = nwarps * PVW;
+  const int s = blockIdx.x, h = blockIdx.y;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, kk = lane / PVW, pp = lane % PVW;
+  const int col = blockIdx.z * pvb + warp * PVW + pp;
+  const int N = p.n_rows, Dv = p.n_cols, H = p.n_heads, g = h / p.heads_per_group;
+  const int chunk = p.chunk;
+  float* k_s = smem;                                         // [chunk][ROWP]
+  float* q_s = k_s + (size_t)chunk * ROWP;
+  float* d_s = q_s + (size_t)chunk * ROWP;                   // row decays (row flavour only)
+  float* v_s = d_s + (ROW_DECAY ? (size_t)chunk * ROWP : 0); // [chunk][pvb]
+  float* a_s = v_s + (size_t)chunk * pvb;                    // [chunk] head decay, [chunk] step size (head flavour)
+  float* dt_s = a_s + chunk;
+
+  float head_a = 0.f, head_dtb = 0.f, head_skip = 0.f;
+  if (!ROW_DECAY) {
+    head_a = -expf(load_any(p.a_log, p.small_dtype, h));
+    head_dtb = p.dt_bias ? load_any(p.dt_bias, p.small_dtype, h) : 0.f;
+  }
+  if (p.skip) head_skip = load_any(p.skip, p.small_dtype, h);
+  pdl_wait();
+  const int n_tok = p.seq_new[s], tok0 = p.seq_tok0[s];
+  const bool live = col < Dv;
+  float* st = p.state + (((size_t)p.seq_slot[s] * H + h) * N) * Dv + col;
+  float S[NPT];
+#pragma unroll
+  for (int i = 0; i < NPT; ++i) {
+    const int n = kk * NPT + i;
+    S[i] = (live && n < N) ? st[(size_t)n * Dv] : 0.f;
+  }
+  for (int c0 = 0; c0 < n_tok; c0 += chunk) {
+    const int nc = min(chunk, n_tok - c0);
+    __syncthreads();                                         // the chunk before has been used
+    for (int e = tid; e < nc * KS * NPT; e += blockDim.x) {
+      const int j = e / (KS * NPT), n = e % (KS * NPT);
+      const int at = j * ROWP + (n / NPT) * (NPT + 4) + n % NPT;
+      const size_t t = (size_t)(tok0 + c0 + j);
+      float kv = 0.f, qv = 0.f, dv = 0.f;
+      if (n < N) {
+        kv = p.k[t * p.k_stride + (size_t)g * N + n];
+        qv = p.q[t * p.q_stride + (size_t)g * N + n] * p.q_scale;
+        if (ROW_DECAY) {
+          float zz = p.z[t * p.z_stride + (size_t)h * N + n];
+          if (p.z_bias) zz += load_any(p.z_bias, p.small_dtype, (size_t)h * N + n);
+          dv = expf(log_sigmoid_f(zz) * p.inv_tau);
+        }
+      }
+      k_s[at] = kv; q_s[at] = qv;
+      if (ROW_DECAY) d_s[at] = dv;
+    }
+    for (int e = tid; e < nc * pvb; e += blockDim.x) {
+      const int j = e / pvb, c = blockIdx.z * pvb + e % pvb;
+      v_s[e] = c < Dv ? p.v[(size_t)(tok0 + c0 + j) * p.v_stride + (size_t)h * Dv + c] : 0.f;
+    }
+    if (!ROW_DECAY) {
+      for (int j = tid; j < nc; j += blockDim.x) {
+        const float dt = softplus_f(p.dt[(size_t)(tok0 + c0 + j) * p.dt_stride + h] + head_dtb);
+        dt_s[j] = dt;
+        a_s[j] = expf(head_a * dt);
+      }
+    }
+    __syncthreads();
+    for (int j = 0; j < nc; ++j) {
+      const float4* k4 = reinterpret_cast<const float4*>(k_s + j * ROWP + kk * (NPT + 4));
+      const float4* q4 = reinterpret_cast<const float4*>(q_s + j * ROWP + kk * (NPT + 4));
+      const float4* d4 = reinterpret_cast<const float4*>(d_s + j * ROWP + kk * (NPT + 4));
+      const float v_raw = v_s[j * pvb + warp * PVW + pp];
+      float vv = v_raw, a = 0.f;
+      if (!ROW_DECAY) { vv = v_raw * dt_s[j]; a = a_s[j]; }
+      float o = 0.f;
+#pragma unroll
+      for (int i4 = 0; i4 < NPT / 4; ++i4) {
+        const float4 kq = k4[i4], qq = q4[i4];
+        float4 dd = make_float4(a, a, a, a);
+        if (ROW_DECAY) dd = d4[i4];
+        S[4 * i4 + 0] = fmaf(kq.x, vv, dd.x * S[4 * i4 + 0]); o = fmaf(S[4 * i4 + 0], qq.x, o);
+        S[4 * i4 + 1] = fmaf(kq.y, vv, dd.y * S[4 * i4 + 1]); o = fmaf(S[4 * i4 + 1], qq.y, o);
+        S[4 * i4 + 2] = fmaf(kq.z, vv, dd.z * S[4 * i4 + 2]); o = fmaf(S[4 * i4 + 2], qq.z, o);
+        S[4 * i4 + 3] = fmaf(kq.w, vv, dd.w * S[4 * i4 + 3]); o = fmaf(S[4 * i4 + 3], qq.w, o);
+      }
+#pragma unroll
+      for (int off = PVW; off < 32; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
+      if (kk == 0 && live)
+        p.out[(size_t)(tok0 + c0 + j) * p.out_stride + (size_t)h * Dv + col] = fmaf(head_skip, v_raw, o);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < NPT; ++i) {
+    const int n = kk * NPT + i;
+    if (live && n < N) st[(size_t)n * Dv] = S[i];
+  }
+}
+
+// ---- gated norm -------------------------------------------------------------------------------------------
+struct GatedNormParams {
+  const float* y; long y_stride;         // [T, width]
+  const float* gate; long gate_stride;   // [T, width] or null
+  const void* w; int w_dtype; int w_len; // weight index = i % w_len (a weight shared by all parts, or one per element)
+  void* out; long out_stride;
+  int width, parts, gate_first; float eps;
+};
+
+template <typename TO>
+__global__ void __launch_bounds__(128) gated_norm_kernel(GatedNormParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[32];
+  const int t = blockIdx.x, part = blockIdx.y, n = p.width / p.parts;
+  const float* y = p.y + (size_t)t * p.y_stride + (size_t)part * n;
+  const float* g = p.gate ? p.gate + (size_t)t * p.gate_stride + (size_t)part * n : nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    float v = y[i];
+    if (g && p.gate_first) v *= silu_f(g[i]);
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)n + p.eps);
+  TO* o = reinterpret_cast<TO*>(p.out) + (size_t)t * p.out_stride + (size_t)part * n;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    float v = y[i];
+    if (g && p.gate_first) v *= silu_f(g[i]);
+    v *= inv;
+    if (p.w) v *= load_any(p.w, p.w_dtype, (size_t)(part * n + i) % p.w_len);
+    if (g && !p.gate_first) v *= silu_f(g[i]);
+    o[i] = from_f32<TO>(v);
+  }
+}
+
+template <int NPT, int KS, bool ROW>
+static int launch_scan(const ScanParams& p0, int n_seqs, cudaStream_t stream) {
+  ScanParams p = p0;
+  constexpr int PVW = 32 / KS, ROWP = KS * (NPT + 4);
+  int nwarps = (p.n_cols + PVW - 1) / PVW;
+  if (nwarps > 2) nwarps = 2;
+  const int pvb = nwarps * PVW;
+  const int per_token = (ROW ? 3 : 2) * ROWP + pvb + 2;
+  int chunk = (40 * 1024 / 4) / per_token;
+  if (chunk > 32) chunk = 32;
+  if (chunk < 1) chunk = 1;
+  p.chunk = chunk;
+  const size_t smem = (size_t)chunk * per_token * sizeof(float);
+  auto kern = linear_scan_kernel<NPT, KS, ROW>;
+  if (smem > 48 * 1024) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+      set_error("linear_scan: %zu bytes of shared memory were refused", smem);
+      return 1;
+    }
+  }
+  dim3 grid(n_seqs, p.n_heads, (p.n_cols + pvb - 1) / pvb);
+  cpi::launch_pdl(kern, grid, dim3(32 * nwarps), smem, stream, p);
+  return check_launch("linear_scan");
+}
+
+template <bool ROW>
+static int dispatch_scan(const ScanParams& p, int n_seqs, cudaStream_t stream) {
+  const int N = p.n_rows;
+  if (N <= 16) return launch_scan<4, 4, ROW>(p, n_seqs, stream);
+  if (N <= 32) return launch_scan<8, 4, ROW>(p, n_seqs, stream);
+  if (N <= 48) return launch_scan<12, 4, ROW>(p, n_seqs, stream);
+  if (N <= 64) return launch_scan<16, 4, ROW>(p, n_seqs, stream);
+  if (N <= 96) return launch_scan<24, 4, ROW>(p, n_seqs, stream);
+  if (N <= 128) return launch_scan<32, 4, ROW>(p, n_seqs, stream);
+  if (N <= 192) return launch_scan<48, 4, ROW>(p, n_seqs, stream);
+  if (N <= 256) return launch_scan<64, 4, ROW>(p, n_seqs, stream);
+  if (N <= 512) return launch_scan<64, 8, ROW>(p, n_seqs, stream);
+  if (N <= 1024) return launch_scan<64, 16, ROW>(p, n_seqs, stream);
+  set_error("linear_scan: a state of %d rows per head is not supported (up to 1024)", N);
+  return 1;
+}
+
+}  // namespace cpi
+
+using namespace cpi;
+
+extern "C" int cpi_causal_conv(const float* in, long in_stride, const void* w, const void* bias, int w_dtype,
+                               float* carry, const int* token_seq, const int* token_pos, const int* seq_slot,
+                               const int* seq_start, const int* seq_tok0, const int* seq_new, float* out,
+                               long out_stride, int n_tokens, int n_seqs, int channels, int taps, int silu,
+                               cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  CPI_REQUIRE(taps >= 1 && taps <= CONV_MAX_TAPS, "causal_conv: %d taps (supported: 1 to %d)", taps, CONV_MAX_TAPS);
+  CPI_REQUIRE(channels > 0 && n_seqs > 0, "causal_conv: bad sizes C=%d sequences=%d", channels, n_seqs);
+  ConvParams p{in, in_stride, w, bias, w_dtype, carry, token_seq, token_pos, seq_slot, seq_start, seq_tok0, seq_new,
+               out, out_stride, channels, taps, silu};
+  const int threads = channels <= 128 ? 128 : 256;
+  cpi::launch_pdl(causal_conv_kernel, dim3(n_tokens, (channels + threads - 1) / threads), threads, 0, stream, p);
+  if (int rc = check_launch("causal_conv")) return rc;
+  if (taps > 1) {
+    cpi::launch_pdl(conv_carry_kernel, dim3(n_seqs, (channels + threads - 1) / threads), threads, 0, stream, p);
+    return check_launch("conv_carry");
+  }
+  return 0;
+}
+
+extern "C" int cpi_linear_scan(const float* k, long k_stride, const float* q, long q_stride, const float* v,
+                               long v_stride, const float* z, long z_stride, const void* z_bias, float inv_tau,
+                               const float* dt, long dt_stride, const void* dt_bias, const void* a_log,
+                               const void* skip, int small_dtype, float q_scale, float* state, float* out,
+                               long out_stride, const int* seq_slot, const int* seq_tok0, const int* seq_new,
+                               int n_seqs, int n_heads, int heads_per_group, int n_rows, int n_cols,
+                               cudaStream_t stream) {
+  if (n_seqs == 0) return 0;
+  CPI_REQUIRE((z != nullptr) != (dt != nullptr), "linear_scan: give row decays or step sizes, one of the two");
+  CPI_REQUIRE(dt == nullptr || a_log != nullptr, "linear_scan: step sizes need the heads' decay rates");
+  CPI_REQUIRE(n_heads > 0 && heads_per_group > 0 && n_heads % heads_per_group == 0 && n_rows > 0 && n_cols > 0,
+              "linear_scan: bad sizes heads=%d per group=%d rows=%d columns=%d", n_heads, heads_per_group, n_rows, n_cols);
+  CPI_REQUIRE(n_heads <= 65535, "linear_scan: too many heads (%d)", n_heads);
+  ScanParams p{k, k_stride, q, q_stride, v, v_stride, z, z_stride, z_bias, inv_tau, dt, dt_stride, dt_bias, a_log,
+               skip, small_dtype, q_scale, state, out, out_stride, seq_slot, seq_tok0, seq_new,
+               n_heads, heads_per_group, n_rows, n_cols, 0};
+  return z ? dispatch_scan<true>(p, n_seqs, stream) : dispatch_scan<false>(p, n_seqs, stream);
+}
+
+extern "C" int cpi_gated_norm(const float* y, long y_stride, const float* gate, long gate_stride, const void* w,
+                              int w_dtype, int w_len, void* out, int out_dtype, long out_stride, int n_tokens,
+                              int width, int parts, int gate_first, float eps, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  CPI_REQUIRE(width > 0 && parts > 0 && width % parts == 0, "gated_norm: %d elements in %d parts", width, parts);
+  CPI_REQUIRE(parts <= 65535, "gated_norm: too many parts (%d)", parts);
+  CPI_REQUIRE(!w || w_len > 0, "gated_norm: a weight needs a length");
+  GatedNormParams p{y, y_stride, gate, gate_stride, w, w_dtype, w_len, out, out_stride, width, parts, gate_first, eps};
+  CPI_DISPATCH_DTYPE(out_dtype, TO, cpi::launch_pdl(gated_norm_kernel<TO>, dim3(n_tokens, parts), 128, 0, stream, p));
+  return check_launch("gated_norm");
+}

@@ -4,6 +4,7 @@ Every array is int32 on the device, filled from one pinned host buffer with a si
   tokens[t]     token id                    token_seq[t]  index of its sequence in this step
   token_pos[t]  absolute position           seq_slot[s]   cache slot of sequence s
   seq_start[s]  positions cached before     seq_new[s]    tokens the step brings for s
+  seq_tok0[s]   packed index of s's first token of the step
   want_rows[r]  packed token indices whose logits are asked for
 """
 from __future__ import annotations
@@ -29,6 +30,7 @@ class StepBatch:
     seq_slot: torch.Tensor
     seq_start: torch.Tensor
     seq_new: torch.Tensor
+    seq_tok0: torch.Tensor
     want_rows: torch.Tensor
     slots: list
     starts: list
@@ -60,7 +62,7 @@ class BatchStager:
     @staticmethod
     def words_needed(n_tokens: int, n_seqs: int, n_want: int) -> int:
         """int32 words a decode step (one token per sequence, no query tiles) stages."""
-        return 3 * n_tokens + 3 * n_seqs + n_want
+        return 3 * n_tokens + 4 * n_seqs + n_want
 
     def _reserve(self, n: int) -> None:
         if n <= self._cap:
@@ -89,7 +91,7 @@ class BatchStager:
                     tiles.append((st + off + rows, base + off, rows))
                 base += n
             tiles.sort(key=lambda x: -x[0])          # most keys first: the long tiles start early
-        total = 3 * T + 3 * B + R + 2 * len(tiles)
+        total = 3 * T + 4 * B + R + 2 * len(tiles)
         self._reserve(total)
         entry = self._ring[self._next]
         self._next = (self._next + 1) % self.RING
@@ -98,16 +100,17 @@ class BatchStager:
             d = static_dev
         if ev is not None:
             ev.synchronize()
-        tokens, token_seq, token_pos, want_rows = [], [], [], []
+        tokens, token_seq, token_pos, want_rows, tok0 = [], [], [], [], []
         base = 0
         for s, (toks, st, w) in enumerate(zip(token_lists, starts, wants)):
             n = len(toks)
+            tok0.append(base)
             tokens += toks
             token_seq += [s] * n
             token_pos += range(st, st + n)
             want_rows += [base + i for i in w]
             base += n
-        flat = (tokens + token_seq + token_pos + list(slots) + list(starts) + n_new + want_rows
+        flat = (tokens + token_seq + token_pos + list(slots) + list(starts) + n_new + tok0 + want_rows
                 + [t[1] for t in tiles] + [t[2] for t in tiles])
         h[:total] = torch.tensor(flat, dtype=torch.int32)
         d[:total].copy_(h[:total], non_blocking=True)
@@ -129,6 +132,6 @@ class BatchStager:
             bucket *= 2
         return StepBatch(n_tokens=T, n_seqs=B, n_want=R, max_new=max(n_new), dtype=dtype, ctx_bucket=bucket,
                          tokens=take(T), token_seq=take(T), token_pos=take(T), seq_slot=take(B),
-                         seq_start=take(B), seq_new=take(B), want_rows=take(R),
+                         seq_start=take(B), seq_new=take(B), seq_tok0=take(B), want_rows=take(R),
                          slots=list(slots), starts=list(starts), n_new=n_new,
                          n_q_tiles=len(tiles), tile_tok0=take(len(tiles)), tile_rows=take(len(tiles)))

@@ -16,6 +16,7 @@ from typing import Optional, Sequence
 import torch
 
 from ..cache import CacheManager
+from ..config.common import read_config_json
 from ..config.registry import apply_overrides, architecture_of, spec_from_model_dir
 from ..config.spec import ModelSpec
 from ..csrc import lib as K
@@ -88,6 +89,9 @@ class Engine:
         cfg, spec = spec_from_model_dir(model_dir, config_overrides)
         src = SafetensorsSource(model_dir)
         try:
+            arch = architecture_of(apply_overrides(read_config_json(model_dir), config_overrides))
+            if arch.refine_spec is not None:
+                spec = arch.refine_spec(cfg, spec, src)
             return cls(spec, src, config=cfg, **kw)
         finally:
             src.close()

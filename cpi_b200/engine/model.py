@@ -23,7 +23,8 @@ class Layer:
     feed_forward_norm: object
 
     def parts(self):
-        return (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward)
+        return tuple(p for p in (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward)
+                     if p is not None)
 
     def all_parts(self):
         """Every object whose code runs in a step of this layer (the mixer's position encoding included)."""
@@ -50,11 +51,18 @@ class DecoderModel:
             self.layers.append(Layer(
                 block=build_part("block", ls.block, ls.prefix),
                 mixer=build_part("mixer", ls.mixer, ls.prefix, workspace=self.ws, owns_cache=i in owners),
-                feed_forward=build_part("feed_forward", ls.feed_forward, ls.prefix, workspace=self.ws),
+                feed_forward=None if ls.feed_forward is None else
+                build_part("feed_forward", ls.feed_forward, ls.prefix, workspace=self.ws),
                 mixer_norm=build_part("norm", ls.mixer_norm, ls.prefix, workspace=self.ws, tag="norm_mixer"),
-                feed_forward_norm=build_part("norm", ls.feed_forward_norm, ls.prefix, workspace=self.ws,
-                                             tag="norm_ffn"),
+                feed_forward_norm=None if ls.feed_forward is None or ls.feed_forward_norm is None else
+                build_part("norm", ls.feed_forward_norm, ls.prefix, workspace=self.ws, tag="norm_ffn"),
             ))
+        self.streams = int(spec.residual_streams)
+        if self.streams < 1:
+            raise ValueError(f"a model keeps at least one residual stream, not {self.streams}")
+        self.logit_scale = float(spec.head.get("logit_scale", 1.0) or 1.0)
+        self.logit_softcap = float(spec.head.get("logit_softcap", 0.0) or 0.0)
+        self.layer_capture = None           # a list: every run appends the residual after each run entry [T, H]
         self.final_norm = build_part("norm", spec.final_norm, "", workspace=self.ws, tag="norm_final")
         self.embed_name = spec.embedding["weight"]
         self.head_name = spec.head["weight"]
@@ -77,7 +85,7 @@ class DecoderModel:
             reqs.append(TensorReq(self.head_name, (V, H)))
         reqs += self.final_norm.requirements()
         for layer in self.layers:
-            for p in layer.parts():
+            for p in (layer.block, *layer.parts()):
                 reqs += p.requirements()
         return reqs
 
@@ -91,7 +99,7 @@ class DecoderModel:
         self.head = self.embedding if self.head_name == self.embed_name else source.get(self.head_name, dev).contiguous()
         self.final_norm.load(source, dev)
         for layer in self.layers:
-            for p in layer.parts():
+            for p in (layer.block, *layer.parts()):
                 p.load(source, dev)
         # the word of the device's error flags that the embedding kernel sets for a token outside the table
         self.err_flag = K.device_error_flags(dev)[1:2] if torch.device(dev).type == "cuda" \
@@ -116,22 +124,34 @@ class DecoderModel:
     # ---- forward ---------------------------------------------------------------------------------
     def run(self, batch, cache_manager) -> torch.Tensor:
         """Runs the step's tokens through every run entry; returns float32 logits [n_want, vocab]."""
-        T, H = batch.n_tokens, self.spec.hidden_size
-        x = self.ws.get("residual", (T, H), torch.float32)
+        T, H, S = batch.n_tokens, self.spec.hidden_size, self.streams
+        # the residual: float32 [T, H], or [S, T, H] for blocks that keep S streams (each starts as the embedding)
+        xs = self.ws.get("residual", (S, T, H), torch.float32)
         with phase("embedding"):
-            K.embedding(batch.tokens, self.embedding, x, self.err_flag)
+            for s in range(S):
+                K.embedding(batch.tokens, self.embedding, xs[s], self.err_flag)
+        x = xs[0] if S == 1 else xs
         for i, e in enumerate(self.spec.run_order):
             layer = self.layers[e.layer]
             owner = i if e.cache_of is None else e.cache_of
             view = parts_base.CacheView(cache_manager, owner, owns=e.cache_of is None)
             layer.block.run(layer, x, batch, view)
+            if self.layer_capture is not None:
+                self.layer_capture.append(xs.sum(0))
         R = batch.n_want
         logits = self.ws.get("logits", (R, self.spec.vocab_size), torch.float32)   # valid until the next step
         if R:
             with phase("rmsnorm"):
-                xn = self.final_norm(x, self.dtype, rows=batch.want_rows)
+                if S == 1:
+                    xn = self.final_norm(x, self.dtype, rows=batch.want_rows)
+                else:                       # the norm of the streams' sum, one kernel
+                    xn = self.ws.get("norm_final", (R, H), self.dtype)
+                    K.hc_step(xs, rows=batch.want_rows, norm_weight=self.final_norm.weight,
+                              norm_offset=self.final_norm.weight_offset, eps=self.final_norm.eps, h_out=xn)
             with phase("lm_head"):
                 project(xn, self.head, logits)
+                if self.logit_scale != 1.0 or self.logit_softcap > 0.0:
+                    K.logit_post(logits, self.logit_scale, self.logit_softcap)
         return logits
 
 

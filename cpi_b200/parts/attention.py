@@ -11,6 +11,14 @@ params: hidden_size, num_heads, num_kv_heads, head_dim, softmax_scale, position 
 qk_norm_eps, qk_norm_order ("before_rope" | "after_rope"), window {"kind", "size"},
 query_temperature (None or {"floor_scale", "attn_scale"}).
 Tensors under the prefix: self_attn.{q,k,v,o}_proj.weight  ([out, in]).
+
+Further parameters, all off by default: value_dim (values of another size than keys), bias (q, k and v
+projections have one), qk_norm_scope "projection" (one RMS norm over all heads of q, one over all of k, with
+weights, before the rotation; "head" is the weightless per-head norm above), sink (a learned number per head whose
+exponential joins the softmax denominator without a key or a value), a position part that rotates only the first
+elements of a head, and tensor_names {"q", "k", "v", "o", "q_bias", "k_bias", "v_bias", "q_norm", "k_norm", "sink"}.
+A mixer that uses one of them prepares q, k and v with the general kernel (`qkv_prepare`), from float32 projection
+rows, so that a row is rounded once, after its norm and rotation.
 """
 from __future__ import annotations
 
@@ -21,7 +29,7 @@ from ..csrc import lib as K
 from ..phases import phase
 from ..weights.store import TensorReq
 from .base import Mixer, RotaryEncoding, ScoreBias, build_part, register_mixer
-from .linear import MODE_ADD, project
+from .linear import MODE_ADD, MODE_STORE, project
 
 
 # set to False to run every attention through the general kernel (tests compare the two families)
@@ -39,8 +47,18 @@ class AttentionMixer(Mixer):
         self.nh, self.nkv, self.d = int(p["num_heads"]), int(p["num_kv_heads"]), int(p["head_dim"])
         if self.nh % self.nkv:
             raise ValueError(f"attention: {self.nh} heads cannot be grouped over {self.nkv} key/value heads")
-        if self.d % 16 or not 16 <= self.d <= 256:
-            raise ValueError(f"attention: head size {self.d} is not supported (multiples of 16 from 16 to 256)")
+        self.dv = int(p.get("value_dim") or self.d)
+        self.bias = bool(p.get("bias", False))
+        self.norm_scope = p.get("qk_norm_scope", "head")
+        if self.norm_scope not in ("head", "projection"):
+            raise ValueError(f"attention: unknown qk_norm_scope '{self.norm_scope}'")
+        self.has_sink = bool(p.get("sink", False))
+        rot = p["position"].get("rotary_dims") if p["position"].kind == "rope" else None
+        self.rot_dims = self.d if rot is None else int(rot)
+        self.general = (self.bias or self.dv != self.d or self.rot_dims != self.d or self.d % 16 != 0
+                        or (bool(p.get("qk_norm", False)) and self.norm_scope == "projection"))
+        if not 1 <= self.d <= 256 or not 1 <= self.dv <= 256 or (not self.general and self.d < 16):
+            raise ValueError(f"attention: head sizes {self.d} / {self.dv} are not supported (up to 256)")
         self.scale = float(p["softmax_scale"])
         self.position = build_part("position", p["position"])
         self.qk_norm = bool(p.get("qk_norm", False))
@@ -55,17 +73,39 @@ class AttentionMixer(Mixer):
         self.ws = workspace
         self.w_qkv = self.w_o = None
         self.rotary = self.score_bias = None
+        self.b_qkv = self.w_qnorm = self.w_knorm = self.sink = None
+        if self.general and (self.temperature is not None or (self.qk_norm and self.norm_scope == "head")
+                             or not self.norm_before_rope and self.qk_norm):
+            raise ValueError("attention: biases, a norm over the whole projection, a partial rotation or values of "
+                             "another size do not combine with the per-head norm, a norm after the rotation or the "
+                             "query temperature")
+        a = "self_attn."
+        self.tn = {"q": a + "q_proj.weight", "k": a + "k_proj.weight", "v": a + "v_proj.weight",
+                   "o": a + "o_proj.weight", "q_bias": a + "q_proj.bias", "k_bias": a + "k_proj.bias",
+                   "v_bias": a + "v_proj.bias", "q_norm": a + "q_norm.weight", "k_norm": a + "k_norm.weight",
+                   "sink": a + "sinks"}
+        self.tn.update(p.get("tensor_names") or {})
+        self.tn = {k: self.prefix + v for k, v in self.tn.items()}
 
     # ---- weights ---------------------------------------------------------------------------------
     def _names(self):
-        a = self.prefix + "self_attn."
-        return a + "q_proj.weight", a + "k_proj.weight", a + "v_proj.weight", a + "o_proj.weight"
+        return self.tn["q"], self.tn["k"], self.tn["v"], self.tn["o"]
 
     def requirements(self):
         q, k, v, o = self._names()
-        reqs = [TensorReq(q, (self.nh * self.d, self.hidden)), TensorReq(o, (self.hidden, self.nh * self.d))]
+        reqs = [TensorReq(q, (self.nh * self.d, self.hidden)), TensorReq(o, (self.hidden, self.nh * self.dv))]
         if self.has_kv:
-            reqs += [TensorReq(k, (self.nkv * self.d, self.hidden)), TensorReq(v, (self.nkv * self.d, self.hidden))]
+            reqs += [TensorReq(k, (self.nkv * self.d, self.hidden)), TensorReq(v, (self.nkv * self.dv, self.hidden))]
+        if self.bias:
+            reqs.append(TensorReq(self.tn["q_bias"], (self.nh * self.d,)))
+            if self.has_kv:
+                reqs += [TensorReq(self.tn["k_bias"], (self.nkv * self.d,)), TensorReq(self.tn["v_bias"], (self.nkv * self.dv,))]
+        if self.qk_norm and self.norm_scope == "projection":
+            reqs.append(TensorReq(self.tn["q_norm"], (self.nh * self.d,), init="ones+normal"))
+            if self.has_kv:
+                reqs.append(TensorReq(self.tn["k_norm"], (self.nkv * self.d,), init="ones+normal"))
+        if self.has_sink:
+            reqs.append(TensorReq(self.tn["sink"], (self.nh,)))
         return reqs
 
     def load(self, source, device):
@@ -77,6 +117,15 @@ class AttentionMixer(Mixer):
         self.w_qkv = torch.cat([t.to(dt) for t in parts], dim=0).contiguous()    # [Q + 2 KV, H]
         del parts
         self.w_o = source.get(o, device).contiguous()
+        if self.bias:
+            names = ["q_bias"] + (["k_bias", "v_bias"] if self.has_kv else [])
+            self.b_qkv = torch.cat([source.get(self.tn[n], device).to(torch.float32) for n in names]).contiguous()
+        if self.qk_norm and self.norm_scope == "projection":
+            self.w_qnorm = source.get(self.tn["q_norm"], device).to(torch.float32).contiguous()
+            if self.has_kv:
+                self.w_knorm = source.get(self.tn["k_norm"], device).to(torch.float32).contiguous()
+        if self.has_sink:
+            self.sink = source.get(self.tn["sink"], device).to(torch.float32).contiguous()
         self.position.prepare(device)
         # what the position part is to this mixer: a rotation of q and k (done with the head norm and the cache
         # write, in one kernel), a bias on the scores (taken by the general attention kernel only), or nothing
@@ -93,34 +142,57 @@ class AttentionMixer(Mixer):
 
     # ---- cache -----------------------------------------------------------------------------------
     def kv_requirement(self):
+        if self.dv != self.d:
+            return KVRequirement(self.nkv, self.d, self.window_kind, self.window_size,
+                                 streams=(("k", self.nkv, self.d), ("v", self.nkv, self.dv)))
         return KVRequirement(self.nkv, self.d, self.window_kind, self.window_size)
 
     # ---- step ------------------------------------------------------------------------------------
-    def forward(self, h, residual, batch, cache):
+    can_store = True          # forward(..., add=False) stores the mixer's output (float32) instead of adding it
+
+    def forward(self, h, residual, batch, cache, add=True):
         T = h.shape[0]
         dt = h.dtype
-        qkv = self.ws.get("attn_qkv", (T, self.w_qkv.shape[0]), dt)
-        with phase("qkv"):
-            project(h, self.w_qkv, qkv)
         k_cache, v_cache, table, page_size = cache.kv()
         q = self.ws.get("attn_q", (T, self.nh * self.d), dt)
-        with phase("kv_store"):          # head norm, rotation, temperature and the write into the cache: one kernel
-            K.qkv_post(qkv, q, k_cache, v_cache, table, page_size, batch.token_seq, batch.token_pos,
-                       batch.seq_slot, n_heads=self.nh, n_kv_heads=self.nkv, head_dim=self.d,
-                       inv_freq=None if self.rotary is None else self.rotary.inv_freq,
-                       interleaved=self.rotary is not None and self.rotary.interleaved,
-                       qk_norm=self.qk_norm, norm_before_rope=self.norm_before_rope,
-                       norm_eps=self.qk_norm_eps, temperature=self.temperature,
-                       write_kv=self.has_kv and cache.owns)
-        att = self.ws.get("attn_out", (T, self.nh * self.d), dt)
+        if self.general:
+            # float32 projection rows: bias, norm and rotation act on unrounded values
+            qkv = self.ws.get("attn_qkv", (T, self.w_qkv.shape[0]), torch.float32)
+            with phase("qkv"):
+                project(h, self.w_qkv, qkv)
+            if self.rotary is not None and self.rotary.interleaved:
+                raise ValueError("attention: the general preparation rotates pairs (i, i + n/2) only")
+            with phase("kv_store"):
+                K.qkv_prepare(qkv, q, k_cache, v_cache, table, page_size, batch.token_seq, batch.token_pos,
+                              batch.seq_slot, n_heads=self.nh, n_kv_heads=self.nkv, head_dim=self.d,
+                              value_dim=self.dv, bias=self.b_qkv, q_norm=self.w_qnorm, k_norm=self.w_knorm,
+                              norm_whole=self.qk_norm, norm_eps=self.qk_norm_eps,
+                              inv_freq=None if self.rotary is None else self.rotary.inv_freq,
+                              rotary_dims=self.rot_dims if self.rotary is not None else 0,
+                              write_kv=self.has_kv and cache.owns)
+        else:
+            qkv = self.ws.get("attn_qkv", (T, self.w_qkv.shape[0]), dt)
+            with phase("qkv"):
+                project(h, self.w_qkv, qkv)
+            with phase("kv_store"):          # head norm, rotation, temperature and the write into the cache: one kernel
+                K.qkv_post(qkv, q, k_cache, v_cache, table, page_size, batch.token_seq, batch.token_pos,
+                           batch.seq_slot, n_heads=self.nh, n_kv_heads=self.nkv, head_dim=self.d,
+                           inv_freq=None if self.rotary is None else self.rotary.inv_freq,
+                           interleaved=self.rotary is not None and self.rotary.interleaved,
+                           qk_norm=self.qk_norm, norm_before_rope=self.norm_before_rope,
+                           norm_eps=self.qk_norm_eps, temperature=self.temperature,
+                           write_kv=self.has_kv and cache.owns)
+        att = self.ws.get("attn_out", (T, self.nh * self.dv), dt)
         with phase("attention"):
             self.attend(q, att, k_cache, v_cache, table, page_size, batch)
         with phase("wo"):
-            project(att, self.w_o, residual, MODE_ADD)
+            project(att, self.w_o, residual, MODE_ADD if add else MODE_STORE)
 
     def attend(self, q, att, k_cache, v_cache, table, page_size, batch):
         wk = K.WINDOW_KINDS[self.window_kind]
-        tensor_cores = use_tensor_core_kernels and self.score_bias is None     # those kernels add nothing to a score
+        # the tensor-core kernels add nothing to a score and take keys and values of one size
+        tensor_cores = (use_tensor_core_kernels and self.score_bias is None and self.sink is None
+                        and self.dv == self.d)
         if (tensor_cores and batch.is_decode and q.dtype == torch.bfloat16
                 and K.attention_decode_supported(self.nh, self.nkv, self.d, page_size)):
             # keys per sequence that the window lets through, at most (a bucketed bound: the split count
@@ -150,4 +222,4 @@ class AttentionMixer(Mixer):
         K.attention_general(q, att, k_cache, v_cache, table, page_size, batch.token_seq, batch.token_pos,
                             batch.seq_slot, n_heads=self.nh, n_kv_heads=self.nkv, head_dim=self.d,
                             window_kind=K.WINDOW_KINDS[self.window_kind], window_size=self.window_size,
-                            scale=self.scale, score_bias=self.score_bias)
+                            scale=self.scale, score_bias=self.score_bias, sink=self.sink, value_dim=self.dv)

@@ -1,8 +1,21 @@
-"""Arrangement of a layer's parts.  "pre_norm": x += mixer(norm1(x)); x += ffn(norm2(x))
-(the order of src/engine/llama4_cpu_engine.cpp:300-329)."""
+"""Arrangements of a layer's parts.
+
+"pre_norm": x += mixer(norm1(x)); x += ffn(norm2(x))  (the order of src/engine/llama4_cpu_engine.cpp:300-329).
+
+"hyper_connections": the residual is S streams x_1 .. x_S (float32 [S, T, H], all equal to the embedding output
+at the start; the final norm reads their sum).  Sublayer q (1: mixer, 2: feed-forward) reads a mixture of the
+streams and writes to all of them:
+    u = sum_s read_q[s] x_s;   y = sublayer_q(norm_q(u));   x_t <- sum_s mix_q[s, t] x_s + write_q[t] y
+(every x_t from the old streams; mix indexed [from, to]).  One kernel per boundary applies the write-back of the
+sublayer before and forms and normalises the next u.  A layer without a feed-forward has the first sublayer only.
+"""
 from __future__ import annotations
 
+import torch
+
+from ..csrc import lib as K
 from ..phases import phase
+from ..weights.store import TensorReq
 from .base import Block, register_block
 
 
@@ -16,6 +29,82 @@ class PreNormBlock(Block):
         with phase("rmsnorm"):
             h = layer.mixer_norm(residual, batch.dtype)
         layer.mixer.forward(h, residual, batch, cache)
+        if layer.feed_forward is None:
+            return
         with phase("rmsnorm"):
             h2 = layer.feed_forward_norm(residual, batch.dtype)
         layer.feed_forward.forward(h2, residual, batch)
+
+
+@register_block("hyper_connections")
+class HyperConnectionsBlock(Block):
+    """params: streams, sublayers (1 or 2), names: per sublayer a dict {"read", "write", "mix"} of tensor names
+    under the layer's prefix, required (False: a missing tensor means ones / the identity, which makes the block
+    the ordinary residual sum).  The layer's norms are the model's norm parts; the block reads their weight,
+    offset and eps and fuses them into its kernel."""
+    graph_safe = True
+
+    def __init__(self, spec, prefix="", **_):
+        super().__init__(spec, prefix)
+        self.S = int(spec["streams"])
+        if not 1 <= self.S <= 8:
+            raise ValueError(f"hyper_connections: {self.S} streams (supported: 1 to 8)")
+        self.names = [dict(n) for n in spec["names"]]
+        self.required = bool(spec.get("required", True))
+        self.coef = []                 # per sublayer (read, write, mix) float32 on the device
+
+    def requirements(self):
+        S, opt = self.S, not self.required
+        reqs = []
+        for n in self.names:
+            reqs += [TensorReq(self.prefix + n["read"], (S,), init=f"const:{1.0 / S}+normal", optional=opt),
+                     TensorReq(self.prefix + n["write"], (S,), init="ones+normal", optional=opt),
+                     TensorReq(self.prefix + n["mix"], (S, S), init="eye+normal", optional=opt)]
+        return reqs
+
+    def load(self, source, device):
+        S = self.S
+        self.coef = []
+        for n in self.names:
+            def get(key, default):
+                name = self.prefix + n[key]
+                if source.has(name):
+                    return source.get(name, device).to(torch.float32).contiguous()
+                return default.to(device)
+            self.coef.append((get("read", torch.ones(S)), get("write", torch.ones(S)), get("mix", torch.eye(S))))
+
+    def _sublayer(self, x, norm, coef, pending, dtype, tag):
+        """Applies the pending write-back (y, coef of the sublayer before) and returns this sublayer's input."""
+        T, H = x.shape[1], x.shape[2]
+        h = norm.ws.get(tag, (T, H), dtype)
+        kw = {} if pending is None else {"y": pending[0], "write": pending[1][1], "mix": pending[1][2]}
+        K.hc_step(x, read=coef[0], norm_weight=norm.weight, norm_offset=norm.weight_offset, eps=norm.eps,
+                  h_out=h, **kw)
+        return h
+
+    @staticmethod
+    def _run_part(part, h, y, *args):
+        """y = part(h): parts that can store their output do; the others add into a zeroed buffer."""
+        if getattr(part, "can_store", False):
+            part.forward(h, y, *args, add=False)
+        else:
+            y.zero_()
+            part.forward(h, y, *args)
+
+    def run(self, layer, residual, batch, cache):
+        x = residual if residual.dim() == 3 else residual.unsqueeze(0)
+        T, H = x.shape[1], x.shape[2]
+        ws = layer.mixer_norm.ws
+        with phase("rmsnorm"):
+            h = self._sublayer(x, layer.mixer_norm, self.coef[0], None, batch.dtype, "norm_mixer")
+        y = ws.get("hc_y", (T, H), torch.float32)
+        self._run_part(layer.mixer, h, y, batch, cache)
+        pending = (y, self.coef[0])
+        if layer.feed_forward is not None:
+            with phase("rmsnorm"):
+                h2 = self._sublayer(x, layer.feed_forward_norm, self.coef[1], pending, batch.dtype, "norm_ffn")
+            y2 = ws.get("hc_y2", (T, H), torch.float32)
+            self._run_part(layer.feed_forward, h2, y2, batch)
+            pending = (y2, self.coef[1])
+        with phase("rmsnorm"):
+            K.hc_step(x, y=pending[0], write=pending[1][1], mix=pending[1][2])

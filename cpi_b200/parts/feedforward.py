@@ -5,7 +5,8 @@ gate_up [H, 2I] and down [I, H] matrices applied as x @ W with a = silu(gate) * 
 expert with ordinary [out, in] matrices, both added to the residual.  The reference takes one expert
 and no gate value; top-k and the sigmoid gate (on the expert's input or output) are parameters here.
 
-dense_swiglu  params: hidden_size, intermediate_size
+dense_swiglu  params: hidden_size, intermediate_size, activation ("silu" by default, or "gelu_tanh": the gate's
+              activation; down(act(gate h) * (up h))), tensor_names (gate, up, down under the prefix)
               tensors: feed_forward.{gate,up,down}_proj.weight
 moe_swiglu    params: hidden_size, num_experts, top_k, expert_size, shared_size (0 = no shared expert),
               router_gate ("sigmoid_input" | "sigmoid_output" | "none")
@@ -46,6 +47,12 @@ class DenseSwiGLU(FeedForward):
                                                                 "feed_forward.down_proj.weight")):
         super().__init__(spec, prefix)
         self.hidden, self.inter = int(spec["hidden_size"]), int(spec["intermediate_size"])
+        self.activation = spec.get("activation", "silu")
+        if self.activation not in K.GATE_ACTS:
+            raise ValueError(f"dense_swiglu: unknown activation '{self.activation}'; known: {sorted(K.GATE_ACTS)}")
+        tn = spec.get("tensor_names")
+        if tn:
+            names = (tn["gate"], tn["up"], tn["down"])
         self.names = tuple(prefix + n for n in names)
         self.ws = workspace
         self.w_gate_up = self.w_down = None
@@ -60,11 +67,19 @@ class DenseSwiGLU(FeedForward):
         self.w_gate_up = _stack(source.get(g, device), source.get(u, device))
         self.w_down = source.get(d, device).contiguous()
 
-    def forward(self, h, residual, batch):
+    can_store = True          # forward(..., add=False) stores the output (float32) instead of adding it
+
+    def forward(self, h, residual, batch, add=True):
         a = self.ws.get("ffn_act", (h.shape[0], self.inter), h.dtype)
         with phase("mlp"):
-            project(h, self.w_gate_up, a, MODE_SWIGLU)
-            project(a, self.w_down, residual, MODE_ADD)
+            if self.activation == "silu":
+                project(h, self.w_gate_up, a, MODE_SWIGLU)
+            else:
+                # the products' fused epilogue knows silu; another activation takes the float32 rows [gate | up]
+                gu = self.ws.get("ffn_gate_up", (h.shape[0], 2 * self.inter), torch.float32)
+                project(h, self.w_gate_up, gu, MODE_STORE)
+                K.gated_act(gu, a, self.activation)
+            project(a, self.w_down, residual, MODE_ADD if add else MODE_STORE)
 
 
 @register_feed_forward("moe_swiglu")

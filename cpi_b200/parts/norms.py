@@ -1,4 +1,5 @@
-"""RMS norm: y = x * rsqrt(mean(x^2) + eps) * w  (src/engine/llama4_cpu_engine.cpp:47-62)."""
+"""RMS norm: y = x * rsqrt(mean(x^2) + eps) * w  (src/engine/llama4_cpu_engine.cpp:47-62); with
+`weight_offset` o the stored weight is a distance from o: y = x * rsqrt(mean(x^2) + eps) * (o + w)."""
 from __future__ import annotations
 
 from ..csrc import lib as K
@@ -8,7 +9,8 @@ from .base import Norm, register_norm
 
 @register_norm("rmsnorm")
 class RMSNorm(Norm):
-    """params: size, eps, weight (tensor name relative to the prefix, or None for a weightless norm)."""
+    """params: size, eps, weight (tensor name relative to the prefix, or None for a weightless norm),
+    weight_offset (0 by default; 1 for a weight stored around zero)."""
     graph_safe = True
 
     def __init__(self, spec, prefix="", workspace=None, tag="norm"):
@@ -16,12 +18,13 @@ class RMSNorm(Norm):
         self.size, self.eps = int(spec["size"]), float(spec["eps"])
         self.weight_name = None if spec.get("weight") is None else prefix + spec["weight"]
         self.weight = None
+        self.weight_offset = float(spec.get("weight_offset", 0.0))
         self.ws, self.tag = workspace, tag
 
     def requirements(self):
         if self.weight_name is None:
             return []
-        return [TensorReq(self.weight_name, (self.size,), init="ones")]
+        return [TensorReq(self.weight_name, (self.size,), init="normal" if self.weight_offset else "ones")]
 
     def load(self, source, device):
         if self.weight_name is not None:
@@ -31,5 +34,5 @@ class RMSNorm(Norm):
         n = x.shape[0] if rows is None else rows.numel()
         if out is None:
             out = self.ws.get(self.tag, (n, self.size), out_dtype)
-        K.rmsnorm(x, self.weight, self.eps, out, rows)
+        K.rmsnorm(x, self.weight, self.eps, out, rows, self.weight_offset)
         return out

@@ -37,7 +37,8 @@ def llama3_frequencies(head_dim: int, theta: float, scaling) -> np.ndarray:
 @register_position("rope")
 class RotaryPosition(Position):
     """params: head_dim, theta, pairing ("half_split" pairs (d, d+D/2); "interleaved" pairs (2d, 2d+1)),
-    scaling (None or the llama3 dictionary)."""
+    scaling (None or the llama3 dictionary), rotary_dims (None: the whole head; n: only the first n elements of a
+    head turn, as pairs (d, d + n/2) with frequencies theta^(-2d/n), the rest pass unchanged)."""
     graph_safe = True
 
     def __init__(self, spec, prefix=""):
@@ -48,7 +49,11 @@ class RotaryPosition(Position):
         if spec["pairing"] not in ("half_split", "interleaved"):
             raise ValueError(f"unknown rope pairing '{spec['pairing']}'")
         self.interleaved = spec["pairing"] == "interleaved"
-        self.frequencies = llama3_frequencies(int(spec["head_dim"]), float(spec["theta"]), sc)
+        dims = spec.get("rotary_dims")
+        dims = int(spec["head_dim"]) if dims is None else int(dims)
+        if dims < 2 or dims % 2 or dims > int(spec["head_dim"]):
+            raise ValueError(f"rope: {dims} rotated elements of a head of {spec['head_dim']}")
+        self.frequencies = llama3_frequencies(dims, float(spec["theta"]), sc)
         self.inv_freq = None
 
     def prepare(self, device):

@@ -1,0 +1,171 @@
+"""Recurrent mixers: what they remember is a fixed-size state per sequence, not a growing cache.
+
+Both keep, per head, a matrix S [rows, columns] in float32 that is updated token by token,
+    S_t = diag(a_t) S_{t-1} + k_t v_t^T,        o_t = S_t^T q_t,
+and differ in where a, k, q and v come from (`csrc/recurrent.cu: linear_scan`).  The state lives in the cache
+manager's per-slot state tensors, is zero when a slot is acquired and is carried across steps, so a prompt may
+come whole, in pieces or token by token.  Decays, step sizes, gates of the recurrence and the state are float32
+in both precisions; the projections feed them as float32 rows.
+
+"mamba2"  selective state space, scalar decay per head:
+          [z | x | B | C | dt] = W_in h;  (x, B, C) <- silu(causal conv over the last `conv` tokens, per channel);
+          dt <- softplus(dt + dt_bias);  a = exp(-exp(A_log) dt);  k = B, q = C (shared by the heads of a group),
+          v = dt x;  y = o + D x;  out = W_o (groupnorm(y * silu(z)) * norm)   -- the gate comes before the norm.
+          params: hidden_size, heads, head_dim (columns), state (rows), groups, conv (taps), norm_groups, norm_eps,
+          tensor_names {"in", "conv", "conv_bias", "dt_bias", "A_log", "D", "norm", "o"}.
+          state: "ssm" [heads, state, head_dim], "conv" [conv - 1, channels] (the last inputs of the convolution).
+"gla"     gated linear attention, a decay per key channel:
+          q = W_q h / sqrt(key_dim), k = W_k h, v = W_v h;  a = sigmoid(W_a2 (W_a1 h) + b)^(1 / tau);
+          out = W_o (concat_heads(rmsnorm(o_head) * norm) * silu(W_g h))   -- norm weight shared by the heads.
+          params: hidden_size, heads, key_dim (rows), value_dim (columns), tau, decay_rank, norm_eps,
+          tensor_names {"q", "k", "v", "g", "o", "norm", "a1", "a2", "a2_bias"}.
+          state: "s" [heads, key_dim, value_dim].
+"""
+from __future__ import annotations
+
+import torch
+
+from ..cache.manager import StateRequirement
+from ..csrc import lib as K
+from ..phases import phase
+from ..weights.store import TensorReq
+from .base import Mixer, register_mixer
+from .linear import MODE_ADD, MODE_STORE, project
+
+
+def _cat_rows(tensors):
+    dt = torch.float32 if any(t.dtype == torch.float32 for t in tensors) else torch.bfloat16
+    return torch.cat([t.to(dt) for t in tensors], dim=0).contiguous()
+
+
+@register_mixer("mamba2")
+class Mamba2Mixer(Mixer):
+    graph_safe = True
+    can_store = True
+
+    def __init__(self, spec, prefix="", workspace=None, owns_cache=True):
+        super().__init__(spec, prefix)
+        p = spec.params
+        self.hidden, self.nh, self.dv = int(p["hidden_size"]), int(p["heads"]), int(p["head_dim"])
+        self.n, self.groups, self.taps = int(p["state"]), int(p["groups"]), int(p["conv"])
+        self.norm_groups, self.eps = int(p.get("norm_groups", 1)), float(p["norm_eps"])
+        self.inner = self.nh * self.dv
+        if self.nh % self.groups:
+            raise ValueError(f"mamba2: {self.nh} heads cannot share {self.groups} groups of B and C")
+        if self.inner % self.norm_groups:
+            raise ValueError(f"mamba2: {self.inner} channels cannot be normed in {self.norm_groups} equal parts")
+        if not 1 <= self.taps <= 8:
+            raise ValueError(f"mamba2: a convolution of {self.taps} taps (supported: 1 to 8)")
+        if not owns_cache:
+            raise ValueError("mamba2: a recurrent layer cannot read another run entry's state")
+        self.channels = self.inner + 2 * self.groups * self.n          # what the convolution runs over
+        self.proj = 2 * self.inner + 2 * self.groups * self.n + self.nh
+        tn = {"in": "mixer.in_proj.weight", "conv": "mixer.conv1d.weight", "conv_bias": "mixer.conv1d.bias",
+              "dt_bias": "mixer.dt_bias", "A_log": "mixer.A_log", "D": "mixer.D", "norm": "mixer.norm.weight",
+              "o": "mixer.out_proj.weight"}
+        tn.update(p.get("tensor_names") or {})
+        self.tn = {k: prefix + v for k, v in tn.items()}
+        self.ws = workspace
+        self.w_in = self.w_conv = self.b_conv = self.dt_bias = self.a_log = self.d_skip = self.w_norm = self.w_o = None
+
+    def requirements(self):
+        t = self.tn
+        return [TensorReq(t["in"], (self.proj, self.hidden)), TensorReq(t["conv"], (self.channels, self.taps)),
+                TensorReq(t["conv_bias"], (self.channels,)), TensorReq(t["dt_bias"], (self.nh,)),
+                TensorReq(t["A_log"], (self.nh,)), TensorReq(t["D"], (self.nh,), init="ones+normal"),
+                TensorReq(t["norm"], (self.inner,), init="ones+normal"), TensorReq(t["o"], (self.hidden, self.inner))]
+
+    def load(self, source, device):
+        t = self.tn
+        f32 = lambda name: source.get(t[name], device).to(torch.float32).contiguous()
+        self.w_in = source.get(t["in"], device).contiguous()
+        self.w_conv, self.b_conv = f32("conv"), f32("conv_bias")
+        self.dt_bias, self.a_log, self.d_skip, self.w_norm = f32("dt_bias"), f32("A_log"), f32("D"), f32("norm")
+        self.w_o = source.get(t["o"], device).contiguous()
+
+    def state_requirements(self):
+        return [StateRequirement("ssm", (self.nh, self.n, self.dv)),
+                StateRequirement("conv", (max(self.taps - 1, 0), self.channels))]
+
+    def forward(self, h, residual, batch, cache, add=True):
+        T, f32 = h.shape[0], torch.float32
+        inner, gn = self.inner, self.groups * self.n
+        proj = self.ws.get("mamba_proj", (T, self.proj), f32)
+        with phase("qkv"):
+            project(h, self.w_in, proj)
+        xbc = self.ws.get("mamba_xbc", (T, self.channels), f32)
+        with phase("kv_store"):
+            K.causal_conv(proj[:, inner:inner + self.channels], self.w_conv, self.b_conv, cache.state("conv"), xbc,
+                          batch, silu=True)
+        y = self.ws.get("mamba_y", (T, inner), f32)
+        with phase("attention"):
+            K.linear_scan(xbc[:, inner:inner + gn], xbc[:, inner + gn:], xbc[:, :inner], cache.state("ssm"), y, batch,
+                          n_heads=self.nh, heads_per_group=self.nh // self.groups, n_rows=self.n, n_cols=self.dv,
+                          dt=proj[:, inner + self.channels:], dt_bias=self.dt_bias, a_log=self.a_log,
+                          skip=self.d_skip)
+            g = self.ws.get("mamba_gated", (T, inner), h.dtype)
+            K.gated_norm(y, proj[:, :inner], self.w_norm, g, parts=self.norm_groups, gate_first=True, eps=self.eps)
+        with phase("wo"):
+            project(g, self.w_o, residual, MODE_ADD if add else MODE_STORE)
+
+
+@register_mixer("gla")
+class GLAMixer(Mixer):
+    graph_safe = True
+    can_store = True
+
+    def __init__(self, spec, prefix="", workspace=None, owns_cache=True):
+        super().__init__(spec, prefix)
+        p = spec.params
+        self.hidden, self.nh = int(p["hidden_size"]), int(p["heads"])
+        self.dk, self.dv = int(p["key_dim"]), int(p["value_dim"])
+        self.tau, self.rank, self.eps = float(p["tau"]), int(p["decay_rank"]), float(p["norm_eps"])
+        if self.tau <= 0:
+            raise ValueError(f"gla: tau must be positive, not {self.tau}")
+        if not owns_cache:
+            raise ValueError("gla: a recurrent layer cannot read another run entry's state")
+        tn = {"q": "mixer.q_proj.weight", "k": "mixer.k_proj.weight", "v": "mixer.v_proj.weight",
+              "g": "mixer.g_proj.weight", "o": "mixer.o_proj.weight", "norm": "mixer.g_norm.weight",
+              "a1": "mixer.gk_proj.0.weight", "a2": "mixer.gk_proj.1.weight", "a2_bias": "mixer.gk_proj.1.bias"}
+        tn.update(p.get("tensor_names") or {})
+        self.tn = {k: prefix + v for k, v in tn.items()}
+        self.ws = workspace
+        self.w_qkvg = self.w_a1 = self.w_a2 = self.b_a2 = self.w_norm = self.w_o = None
+
+    def requirements(self):
+        t, H, nk, nv = self.tn, self.hidden, self.nh * self.dk, self.nh * self.dv
+        return [TensorReq(t["q"], (nk, H)), TensorReq(t["k"], (nk, H)), TensorReq(t["v"], (nv, H)),
+                TensorReq(t["g"], (nv, H)), TensorReq(t["o"], (H, nv)), TensorReq(t["norm"], (self.dv,), init="ones+normal"),
+                TensorReq(t["a1"], (self.rank, H)), TensorReq(t["a2"], (nk, self.rank)), TensorReq(t["a2_bias"], (nk,))]
+
+    def load(self, source, device):
+        t = self.tn
+        self.w_qkvg = _cat_rows([source.get(t[n], device) for n in ("q", "k", "v", "g")])
+        self.w_a1 = source.get(t["a1"], device).contiguous()
+        self.w_a2 = source.get(t["a2"], device).contiguous()
+        self.b_a2 = source.get(t["a2_bias"], device).to(torch.float32).contiguous()
+        self.w_norm = source.get(t["norm"], device).to(torch.float32).contiguous()
+        self.w_o = source.get(t["o"], device).contiguous()
+
+    def state_requirements(self):
+        return [StateRequirement("s", (self.nh, self.dk, self.dv))]
+
+    def forward(self, h, residual, batch, cache, add=True):
+        T, f32 = h.shape[0], torch.float32
+        nk, nv = self.nh * self.dk, self.nh * self.dv
+        proj = self.ws.get("gla_proj", (T, 2 * nk + 2 * nv), f32)
+        low = self.ws.get("gla_low", (T, self.rank), h.dtype)
+        z = self.ws.get("gla_z", (T, nk), f32)
+        with phase("qkv"):
+            project(h, self.w_qkvg, proj)
+            project(h, self.w_a1, low)
+            project(low, self.w_a2, z)
+        o = self.ws.get("gla_o", (T, nv), f32)
+        with phase("attention"):
+            K.linear_scan(proj[:, nk:2 * nk], proj[:, :nk], proj[:, 2 * nk:2 * nk + nv], cache.state("s"), o, batch,
+                          n_heads=self.nh, heads_per_group=1, n_rows=self.dk, n_cols=self.dv, z=z, z_bias=self.b_a2,
+                          tau=self.tau, q_scale=self.dk ** -0.5)
+            g = self.ws.get("gla_gated", (T, nv), h.dtype)
+            K.gated_norm(o, proj[:, 2 * nk + nv:], self.w_norm, g, parts=self.nh, gate_first=False, eps=self.eps)
+        with phase("wo"):
+            project(g, self.w_o, residual, MODE_ADD if add else MODE_STORE)

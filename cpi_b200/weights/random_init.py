@@ -92,9 +92,30 @@ class RandomSource(WeightSource):
     def get(self, name, device):
         r = self.reqs[name]
         device = torch.device(device)
-        if r.init == "ones":
-            return torch.ones(r.shape, dtype=self.dtype, device=device)
+        # an init rule is a sum of terms joined by "+": "normal" (the counter-based draw), "ones", "zeros",
+        # "eye" (a square matrix), "const:<value>"
+        terms = r.init.split("+")
+        fixed = None
+        for term in terms:
+            if term == "normal":
+                continue
+            if term == "ones":
+                c = torch.ones(r.shape, dtype=torch.float32, device=device)
+            elif term == "zeros":
+                c = torch.zeros(r.shape, dtype=torch.float32, device=device)
+            elif term == "eye":
+                c = torch.eye(r.shape[0], r.shape[1], dtype=torch.float32, device=device)
+            elif term.startswith("const:"):
+                c = torch.full(r.shape, float(term[6:]), dtype=torch.float32, device=device)
+            else:
+                raise ValueError(f"tensor '{name}': unknown init rule '{r.init}'")
+            fixed = c if fixed is None else fixed + c
+        if "normal" not in terms:
+            return fixed.to(self.dtype)
         ts = _tensor_seed(self.seed, name)
+        if fixed is not None:
+            flat = counter_normal(ts, 0, fixed.numel(), self.std, device).view(r.shape)
+            return (fixed + flat).to(self.dtype)
         out = torch.empty(r.shape, dtype=self.dtype, device=device)
         if device.type == "cuda" and self.dtype in (torch.bfloat16, torch.float32):
             # on a GPU the kernel library draws the tensor in place: the same integer arithmetic, the same bits

@@ -34,7 +34,7 @@ class TensorReq:
     """A tensor a part needs: full name, shape, how a random model fills it."""
     name: str
     shape: tuple
-    init: str = "normal"        # "normal" (std = initializer range) or "ones"
+    init: str = "normal"        # "normal" (std = initializer range), "ones", "zeros", "eye", "const:<v>", or a sum "a+b"
     optional: bool = False      # absent is fine; the part asks `source.has(name)`
 
 
