@@ -38,6 +38,7 @@ struct Params {
   int n_splits;
   float* part_o; float* part_ml;                    // [T, NH, splits, D], [T, NH, splits, 2]
   int* error_flag;                                  // set to 1 when a wait on the copy engine ran out
+  const float* sink;                                // [NH] float32 or null: exp(sink[h]) joins the denominator
 };
 
 constexpr uint32_t kSpinLimit = 1u << 24;
@@ -106,10 +107,16 @@ template <int D> __device__ __forceinline__ int tile_off(int row, int chunk) {
 // the block that takes a group's last ticket, was measured slower at every batch size: one block then
 // merges all the heads of its group one after the other.)
 constexpr int kMaxSplits = 256;
+// What a sink adds to a softmax denominator whose terms are 2^(score - M): 2^(sink - M), the sink given in the
+// same base-2 units (sink * log2 e, unscaled); a number below -1e29 means there is none.  The exponent is capped
+// so that a sink far above every score gives a huge finite denominator (the output then rounds to zero).
+__device__ __forceinline__ float sink_term(float sink_l2, float M) {
+  return sink_l2 < -1e29f ? 0.f : exp2f(fminf(sink_l2 - M, 120.f));
+}
 struct CombineSmem { float w[kMaxSplits], wl[kMaxSplits], red[4]; };
 __device__ __forceinline__ void combine_head(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                              __nv_bfloat16* __restrict__ out, size_t th, int n_splits, int D,
-                                             CombineSmem& sm) {
+                                             CombineSmem& sm, float sink_l2 = -1e30f) {
   const int tid = threadIdx.x, n_warps = blockDim.x >> 5;
   const float2* ml = reinterpret_cast<const float2*>(part_ml) + th * n_splits;
   const float* po = part_o + th * n_splits * D;
@@ -136,6 +143,7 @@ __device__ __forceinline__ void combine_head(const float* __restrict__ part_o, c
         acc += f * v[s];
       }
     }
+    L += sink_term(sink_l2, M);
     if (mine) out[th * D + tid] = __float2bfloat16_rn(acc / fmaxf(L, 1e-20f));
     return;
   }
@@ -165,6 +173,7 @@ __device__ __forceinline__ void combine_head(const float* __restrict__ part_o, c
   __syncthreads();
   float L = 0.f;
   for (int s = 0; s < n_splits; ++s) L += sm.wl[s];
+  L += sink_term(sink_l2, M);
   for (int d = tid; d < D; d += blockDim.x) {
     float acc = 0.f;
     for (int s0 = 0; s0 < n_splits; s0 += 8) {
@@ -387,6 +396,7 @@ __global__ void __launch_bounds__(NT) attention_decode_kernel(const __grid_const
     }
     const int head = kvh * G + g;
     if (p.n_splits == 1) {
+      if (p.sink) L += sink_term(p.sink[head] * 1.4426950408889634f, M);
       p.out[((size_t)t * p.n_heads + head) * D + d] = __float2bfloat16_rn(acc / fmaxf(L, 1e-20f));
     } else {
       const size_t pi = ((size_t)t * p.n_heads + head) * p.n_splits + split;
@@ -397,11 +407,13 @@ __global__ void __launch_bounds__(NT) attention_decode_kernel(const __grid_const
 }
 
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                         __nv_bfloat16* __restrict__ out, int n_splits, int D) {
+                                         __nv_bfloat16* __restrict__ out, int n_splits, int D,
+                                         const float* __restrict__ sink, int n_heads) {
   __shared__ CombineSmem sm;
   pdl_launch_dependents();
+  const float sink_l2 = sink ? sink[blockIdx.x % n_heads] * 1.4426950408889634f : -1e30f;      // a weight: before the wait
   pdl_wait();
-  combine_head(part_o, part_ml, out, blockIdx.x, n_splits, D, sm);
+  combine_head(part_o, part_ml, out, blockIdx.x, n_splits, D, sm, sink_l2);
 }
 
 }  // namespace dec
@@ -443,7 +455,7 @@ extern "C" int cpi_attention_decode(const void* q, void* out, const void* k_cach
                                     const int* token_pos, const int* seq_slot, int n_tokens, int n_heads,
                                     int n_kv_heads, int head_dim, int window_kind, int window_size, float scale,
                                     int n_splits, float* part_o, float* part_ml, int* error_flag,
-                                    cudaStream_t stream) {
+                                    const float* sink, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   CPI_REQUIRE(cpi_attention_decode_supported(n_heads, n_kv_heads, head_dim, page_size),
               "attention_decode: unsupported shape (heads %d/%d, head size %d, page %d)", n_heads, n_kv_heads, head_dim, page_size);
@@ -454,7 +466,7 @@ extern "C" int cpi_attention_decode(const void* q, void* out, const void* k_cach
               "attention_decode: the cache must hold at least one page and be 16-byte aligned");
   dec::Params p{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
                 page_table, max_blocks, token_seq, token_pos, seq_slot, n_heads, n_kv_heads, window_kind, window_size,
-                scale * 1.4426950408889634f, n_splits, part_o, part_ml, error_flag};
+                scale * 1.4426950408889634f, n_splits, part_o, part_ml, error_flag, sink};
   // the cache as rows of head_dim features: a (page, head) tile is 64 consecutive rows
   CUtensorMap mk, mv;
   const uint64_t kv_rows = (uint64_t)n_pages * n_kv_heads * dec::PAGE;
@@ -477,7 +489,7 @@ extern "C" int cpi_attention_decode(const void* q, void* out, const void* k_cach
   if (check_launch("attention_decode")) return 2;
   if (n_splits > 1) {
     cpi::launch_pdl(dec::attention_combine_kernel, n_tokens * n_heads, head_dim <= 64 ? 64 : 128, 0, stream, 
-        part_o, part_ml, (__nv_bfloat16*)out, n_splits, head_dim);
+        part_o, part_ml, (__nv_bfloat16*)out, n_splits, head_dim, sink, n_heads);
     return check_launch("attention_combine");
   }
   return 0;
@@ -544,5 +556,5 @@ extern "C" int cpi_attention_decode_noalloc(const void* q, void* out, const void
   float* part_ml = scratch + (long)n_tokens * n_heads * n_splits * head_dim;
   return cpi_attention_decode(q, out, k_cache, v_cache, n_pages, page_table, max_blocks, page_size, token_seq,
                               token_pos, seq_slot, n_tokens, n_heads, n_kv_heads, head_dim, window_kind, window_size,
-                              scale, n_splits, part_o, part_ml, nullptr, stream);
+                              scale, n_splits, part_o, part_ml, nullptr, nullptr, stream);
 }

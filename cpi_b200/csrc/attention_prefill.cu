@@ -45,6 +45,7 @@ struct Params {
   int window_kind, window_size;
   float scale_log2;
   int* error_flag;
+  const float* sink;                  // [NH] float32 or null: exp(sink[h]) joins the softmax denominator (no key, no value)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -497,6 +498,9 @@ __global__ void __launch_bounds__(320) attention_prefill_kernel(const __grid_con
     ok = __all_sync(0xffffffffu, ok && mbar_wait(&o_done[x], 0, abort_flag));
     fence_after_sync();
     if (ok) {
+      // a sink adds 2^(sink log2 e - reference) to the row's sum and nothing to O; the exponent is capped so that a
+      // sink far above every score gives a huge finite sum
+      if (p.sink) l_run += exp2f(fminf(p.sink[head] * 1.4426950408889634f - m_ref, 120.f));
       const float inv = 1.0f / fmaxf(l_run, 1e-20f);
       __nv_bfloat16* dst = p.out + ((size_t)(tok0 + x * BQ + row) * p.n_heads + head) * D;
 #pragma unroll 1
@@ -545,7 +549,7 @@ extern "C" int cpi_attention_prefill(const void* q, void* out, const void* k_cac
                                      const int* token_pos, const int* seq_slot, const int* tile_tok0,
                                      const int* tile_rows, int n_tiles, int n_tokens, int n_heads, int n_kv_heads,
                                      int head_dim, int window_kind, int window_size, float scale, int* error_flag,
-                                     cudaStream_t stream) {
+                                     const float* sink, cudaStream_t stream) {
   if (n_tiles == 0) return 0;
   CPI_REQUIRE(cpi_attention_prefill_supported(n_heads, n_kv_heads, head_dim, page_size),
               "attention_prefill: unsupported shape (heads %d/%d, head size %d, page %d)", n_heads, n_kv_heads, head_dim, page_size);
@@ -558,7 +562,7 @@ extern "C" int cpi_attention_prefill(const void* q, void* out, const void* k_cac
   if (tc::get_map_2d_bf16(k_cache, (uint64_t)head_dim, kv_rows, (uint64_t)head_dim * 2, 64, pre::PAGE, &mk)) return 1;
   if (tc::get_map_2d_bf16(v_cache, (uint64_t)head_dim, kv_rows, (uint64_t)head_dim * 2, 64, pre::PAGE, &mv)) return 1;
   pre::Params p{(__nv_bfloat16*)out, page_table, max_blocks, token_pos, token_seq, seq_slot, tile_tok0, tile_rows,
-                n_heads, n_kv_heads, window_kind, window_size, scale * 1.4426950408889634f, error_flag};
+                n_heads, n_kv_heads, window_kind, window_size, scale * 1.4426950408889634f, error_flag, sink};
   dim3 grid(n_heads, n_tiles);
   const int halves = head_dim / 64;
   const int smem = halves * 128 * 128 * (2 + pre::kRingSlots);     // Q of both tiles, the ring of K and V tiles

@@ -25,6 +25,7 @@ struct GemmParams {
   const float* row_scale;
   const int* group_offsets; int n_groups;
   int M, N, K;
+  int gate_act;      // gated mode: the gate's activation (0 silu, 1 gelu in its tanh form)
 };
 
 constexpr int BN = 64, BK = 16, NT = 256;
@@ -126,7 +127,8 @@ __global__ void __launch_bounds__(NT) gemm_simt_kernel(GemmParams p) {
       float v = acc[i][j] * s;
       if (MODE == kSwiglu) {
         const float u = acc2[i][j] * s;
-        v = v / (1.0f + expf(-v)) * u;
+        v = (p.gate_act ? 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)))
+                        : v / (1.0f + expf(-v))) * u;
         o[n] = from_f32<TO>(v);
       } else if (MODE == kAdd) {
         o[n] = from_f32<TO>(to_f32(o[n]) + v);
@@ -174,10 +176,12 @@ extern "C" int cpi_gemm_simt(const void* a, int a_dtype, long lda, const int* a_
                              const float* row_scale, const int* group_offsets, int n_groups,
                              int M, int N, int K, int mode, int rows_per_group_hint, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
+  const int gate_act = mode == 3 ? 1 : 0;          // mode 3: the gated mode with a gelu gate
+  if (mode == 3) mode = 2;
   CPI_REQUIRE(M > 0 && N > 0 && K > 0, "gemm: bad sizes M=%d N=%d K=%d", M, N, K);
   CPI_REQUIRE(mode != kAdd || out_dtype == kF32, "gemm: ADD mode needs a float32 output");
   GemmParams p{a, lda, a_rows, w, ldw, w_group_stride, out, ldo, out_rows, row_scale,
-               group_offsets, n_groups, M, N, K};
+               group_offsets, n_groups, M, N, K, gate_act};
   CPI_DISPATCH_DTYPE(a_dtype, TA, CPI_DISPATCH_DTYPE(w_dtype, TW, CPI_DISPATCH_DTYPE(out_dtype, TO,
       return (launch_mode<TA, TW, TO>(p, mode, rows_per_group_hint, stream)))));
   return 0;

@@ -13,7 +13,8 @@ import torch
 from . import build as _build
 
 F32, BF16 = 0, 1
-MODE_STORE, MODE_ADD, MODE_SWIGLU = 0, 1, 2
+MODE_STORE, MODE_ADD, MODE_SWIGLU, MODE_GEGLU = 0, 1, 2, 3      # GEGLU: the gated mode with a gelu (tanh form) gate
+GATED_MODES = (MODE_SWIGLU, MODE_GEGLU)
 WINDOW_FULL, WINDOW_CHUNK, WINDOW_SLIDING = 0, 1, 2
 WINDOW_KINDS = {"full": WINDOW_FULL, "chunk": WINDOW_CHUNK, "sliding": WINDOW_SLIDING}
 MAX_DECODE_SPLITS = 256          # key splits that the combine kernel of decode attention takes
@@ -127,8 +128,8 @@ def gemm_simt(a, w, out, mode=MODE_STORE, *, n_out=None, m_rows=None, a_rows=Non
         _rowmajor(w, "gemm w")
         rows_w, stride_g = w.shape[0], 0
     assert w.shape[-1] == K, f"gemm: a has K={K}, w has K={w.shape[-1]}"
-    N = n_out if n_out is not None else (rows_w // 2 if mode == MODE_SWIGLU else rows_w)
-    assert rows_w == (2 * N if mode == MODE_SWIGLU else N)
+    N = n_out if n_out is not None else (rows_w // 2 if mode in GATED_MODES else rows_w)
+    assert rows_w == (2 * N if mode in GATED_MODES else N)
     assert out.shape[1] == N
     M = m_rows if m_rows is not None else (a_rows.numel() if a_rows is not None else a.shape[0])
     ldw = w.stride(-2)
@@ -176,15 +177,15 @@ def gemm_tc(a, w, out, mode=MODE_STORE, *, n_out=None, m_rows=None, a_rows=None,
     K = a.shape[1]
     if K % 8 or a.stride(0) % 8 or a.data_ptr() % 16 or w.data_ptr() % 16 or w.shape[-1] != K:
         return False
-    if mode == MODE_SWIGLU and out.dtype != torch.bfloat16:
+    if mode in GATED_MODES and out.dtype != torch.bfloat16:
         return False
     if mode == MODE_ADD and out.dtype != torch.float32:
         return False
     _need_cuda(a, w, out, out_rows, row_scale, group_offsets)
     grouped = group_offsets is not None
     rows_w = w.shape[-2]
-    N = n_out if n_out is not None else (rows_w // 2 if mode == MODE_SWIGLU else rows_w)
-    if rows_w != (2 * N if mode == MODE_SWIGLU else N) or out.shape[1] != N:
+    N = n_out if n_out is not None else (rows_w // 2 if mode in GATED_MODES else rows_w)
+    if rows_w != (2 * N if mode in GATED_MODES else N) or out.shape[1] != N:
         raise KernelError(f"gemm_tc: weight rows {rows_w} do not match {N} outputs in mode {mode}")
     if grouped and (w.dim() != 3 or w.shape[0] != n_groups):
         raise KernelError("gemm_tc: grouped weights must be [groups, rows, K]")
@@ -193,7 +194,7 @@ def gemm_tc(a, w, out, mode=MODE_STORE, *, n_out=None, m_rows=None, a_rows=None,
         raise KernelError("gemm_tc: more logical rows than activation rows")
     bn, splits, live_y = c_int(), c_int(), c_int()
     load().cpi_gemm_tc_plan(c_int(T), c_int(N), c_int(K), c_int(n_groups if grouped else 0),
-                            c_int(int(mode == MODE_SWIGLU)), ctypes.byref(bn), ctypes.byref(splits),
+                            c_int(int(mode in GATED_MODES)), ctypes.byref(bn), ctypes.byref(splits),
                             ctypes.byref(live_y))
     _call("cpi_gemm_tc", _p(a), c_long(a.stride(0)), _p(w), _p(out), c_int(dtype_code(out.dtype)),
           c_long(out.stride(0)), _p(out_rows), _p(row_scale), _p(group_offsets), c_int(n_groups if grouped else 0),
@@ -236,14 +237,14 @@ def gemm_tc_pair(a, w, out, mode=MODE_STORE, *, m_rows=None, out_rows=None, row_
     K = a.shape[1]
     T = m_rows if m_rows is not None else a.shape[0]
     rows_w = w.shape[-2]
-    N = rows_w // 2 if mode == MODE_SWIGLU else rows_w
+    N = rows_w // 2 if mode in GATED_MODES else rows_w
     if w.shape[-1] != K or out.shape[1] != N or a.stride(0) % 8 or a.data_ptr() % 16 or w.data_ptr() % 16:
         return False
     if grouped and w.shape[0] != n_groups:
         return False
-    if (mode == MODE_SWIGLU and out.dtype != torch.bfloat16) or (mode == MODE_ADD and out.dtype != torch.float32):
+    if (mode in GATED_MODES and out.dtype != torch.bfloat16) or (mode == MODE_ADD and out.dtype != torch.float32):
         return False
-    bn = load().cpi_gemm_tc_pair_plan(c_int(T), c_int(N), c_int(K), c_int(int(mode == MODE_SWIGLU)),
+    bn = load().cpi_gemm_tc_pair_plan(c_int(T), c_int(N), c_int(K), c_int(int(mode in GATED_MODES)),
                                       c_int(n_groups if grouped else 0))
     if bn <= 0:
         return False
@@ -470,9 +471,11 @@ def attention_decode_supported(n_heads, n_kv_heads, head_dim, page_size) -> bool
 
 
 def attention_decode(q, out, k_cache, v_cache, page_table, page_size, token_seq, token_pos, seq_slot, *,
-                     n_heads, n_kv_heads, head_dim, window_kind, window_size, scale, n_splits):
-    """bfloat16 attention of independent tokens against the paged cache, keys split over `n_splits` blocks."""
-    _need_cuda(q, out, k_cache, v_cache, page_table, token_seq, token_pos, seq_slot)
+                     n_heads, n_kv_heads, head_dim, window_kind, window_size, scale, n_splits, sink=None):
+    """bfloat16 attention of independent tokens against the paged cache, keys split over `n_splits` blocks.
+    `sink`: float32 [heads] whose exponentials join the softmax denominators."""
+    _need_cuda(q, out, k_cache, v_cache, page_table, token_seq, token_pos, seq_slot, sink)
+    assert sink is None or (sink.dtype == torch.float32 and sink.is_contiguous() and sink.numel() == n_heads)
     assert q.is_contiguous() and out.is_contiguous() and q.dtype == out.dtype == k_cache.dtype == torch.bfloat16
     T = q.shape[0]
     po = pml = None
@@ -490,7 +493,7 @@ def attention_decode(q, out, k_cache, v_cache, page_table, page_size, token_seq,
     _call("cpi_attention_decode", _p(q), _p(out), _p(k_cache), _p(v_cache), c_long(k_cache.shape[0]), _p(page_table),
           c_int(page_table.shape[1]), c_int(page_size), _p(token_seq), _p(token_pos), _p(seq_slot), c_int(T),
           c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_int(window_kind), c_int(window_size), c_float(scale),
-          c_int(n_splits), _p(po), _p(pml), _p(tc_error_flag(q.device)), _stream())
+          c_int(n_splits), _p(po), _p(pml), _p(tc_error_flag(q.device)), _p(sink), _stream())
 
 
 def attention_decode_blocks_per_sm(head_dim: int) -> int:
@@ -504,16 +507,18 @@ def attention_prefill_supported(n_heads, n_kv_heads, head_dim, page_size) -> boo
 
 
 def attention_prefill(q, out, k_cache, v_cache, page_table, page_size, token_seq, token_pos, seq_slot, tile_tok0,
-                      tile_rows, *, n_heads, n_kv_heads, head_dim, window_kind, window_size, scale):
-    """bfloat16 attention of query tiles (<= PREFILL_TILE_ROWS consecutive tokens of one sequence each) on tcgen05."""
-    _need_cuda(q, out, k_cache, v_cache, page_table, token_seq, token_pos, seq_slot, tile_tok0, tile_rows)
+                      tile_rows, *, n_heads, n_kv_heads, head_dim, window_kind, window_size, scale, sink=None):
+    """bfloat16 attention of query tiles (<= PREFILL_TILE_ROWS consecutive tokens of one sequence each) on tcgen05.
+    `sink`: float32 [heads] whose exponentials join the softmax denominators."""
+    _need_cuda(q, out, k_cache, v_cache, page_table, token_seq, token_pos, seq_slot, tile_tok0, tile_rows, sink)
+    assert sink is None or (sink.dtype == torch.float32 and sink.is_contiguous() and sink.numel() == n_heads)
     assert q.is_contiguous() and out.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous()
     assert q.dtype == out.dtype == k_cache.dtype == torch.bfloat16
     _call("cpi_attention_prefill", _p(q), _p(out), _p(k_cache), _p(v_cache), c_long(k_cache.shape[0]), _p(page_table),
           c_int(page_table.shape[1]), c_int(page_size), _p(token_seq), _p(token_pos), _p(seq_slot), _p(tile_tok0),
           _p(tile_rows), c_int(tile_tok0.numel()), c_int(q.shape[0]), c_int(n_heads), c_int(n_kv_heads),
           c_int(head_dim), c_int(window_kind), c_int(window_size), c_float(scale), _p(tc_error_flag(q.device)),
-          _stream())
+          _p(sink), _stream())
 
 
 def router_topk(h, w, topk_idx, topk_gate, *, top_k, sigmoid_gate, logits_out=None):

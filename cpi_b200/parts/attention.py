@@ -191,8 +191,7 @@ class AttentionMixer(Mixer):
     def attend(self, q, att, k_cache, v_cache, table, page_size, batch):
         wk = K.WINDOW_KINDS[self.window_kind]
         # the tensor-core kernels add nothing to a score and take keys and values of one size
-        tensor_cores = (use_tensor_core_kernels and self.score_bias is None and self.sink is None
-                        and self.dv == self.d)
+        tensor_cores = use_tensor_core_kernels and self.score_bias is None and self.dv == self.d
         if (tensor_cores and batch.is_decode and q.dtype == torch.bfloat16
                 and K.attention_decode_supported(self.nh, self.nkv, self.d, page_size)):
             # keys per sequence that the window lets through, at most (a bucketed bound: the split count
@@ -210,14 +209,15 @@ class AttentionMixer(Mixer):
             n_splits = max(1, min(want, pages // 4, K.MAX_DECODE_SPLITS))    # a block takes four pages or more
             K.attention_decode(q, att, k_cache, v_cache, table, page_size, batch.token_seq, batch.token_pos,
                                batch.seq_slot, n_heads=self.nh, n_kv_heads=self.nkv, head_dim=self.d,
-                               window_kind=wk, window_size=self.window_size, scale=self.scale, n_splits=n_splits)
+                               window_kind=wk, window_size=self.window_size, scale=self.scale, n_splits=n_splits,
+                               sink=self.sink)
             return
         if (tensor_cores and not batch.is_decode and q.dtype == torch.bfloat16 and batch.n_q_tiles
                 and K.attention_prefill_supported(self.nh, self.nkv, self.d, page_size)):
             K.attention_prefill(q, att, k_cache, v_cache, table, page_size, batch.token_seq, batch.token_pos,
                                 batch.seq_slot, batch.tile_tok0, batch.tile_rows, n_heads=self.nh,
                                 n_kv_heads=self.nkv, head_dim=self.d, window_kind=wk, window_size=self.window_size,
-                                scale=self.scale)
+                                scale=self.scale, sink=self.sink)
             return
         K.attention_general(q, att, k_cache, v_cache, table, page_size, batch.token_seq, batch.token_pos,
                             batch.seq_slot, n_heads=self.nh, n_kv_heads=self.nkv, head_dim=self.d,

@@ -24,7 +24,7 @@ from ..csrc import lib as K
 from ..phases import active as phases_active, phase
 from ..weights.store import TensorReq
 from .base import FeedForward, register_feed_forward
-from .linear import MODE_ADD, MODE_STORE, MODE_SWIGLU, project
+from .linear import MODE_ADD, MODE_GEGLU, MODE_STORE, MODE_SWIGLU, project
 
 
 def _stack(a, b):
@@ -72,13 +72,8 @@ class DenseSwiGLU(FeedForward):
     def forward(self, h, residual, batch, add=True):
         a = self.ws.get("ffn_act", (h.shape[0], self.inter), h.dtype)
         with phase("mlp"):
-            if self.activation == "silu":
-                project(h, self.w_gate_up, a, MODE_SWIGLU)
-            else:
-                # the products' fused epilogue knows silu; another activation takes the float32 rows [gate | up]
-                gu = self.ws.get("ffn_gate_up", (h.shape[0], 2 * self.inter), torch.float32)
-                project(h, self.w_gate_up, gu, MODE_STORE)
-                K.gated_act(gu, a, self.activation)
+            # the gate's activation and the product with `up` happen in the epilogue of the first product
+            project(h, self.w_gate_up, a, MODE_SWIGLU if self.activation == "silu" else MODE_GEGLU)
             project(a, self.w_down, residual, MODE_ADD if add else MODE_STORE)
 
 

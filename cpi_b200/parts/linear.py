@@ -10,7 +10,7 @@ import torch
 
 from ..csrc import lib as K
 
-MODE_STORE, MODE_ADD, MODE_SWIGLU = K.MODE_STORE, K.MODE_ADD, K.MODE_SWIGLU
+MODE_STORE, MODE_ADD, MODE_SWIGLU, MODE_GEGLU = K.MODE_STORE, K.MODE_ADD, K.MODE_SWIGLU, K.MODE_GEGLU
 
 # set to False to force the FP32-pipe kernel everywhere (tests compare the two)
 use_tensor_cores = True

@@ -245,6 +245,23 @@ def test_gated_norm_gelu_gate_and_logit_cap_kernels():
     assert (lg.double() - ref).abs().max() < 1e-5
 
 
+@pytest.mark.parametrize("T,I,H,dtype", [(5, 72, 40, torch.float32), (40, 200, 136, torch.bfloat16),
+                                         (600, 256, 128, torch.bfloat16)])
+def test_gelu_gate_in_the_product_epilogue(T, I, H, dtype):
+    """out = gelu_tanh(h Wg^T) * (h Wu^T) from one product over [Wg; Wu], on the float32 pipe, on the tensor-core
+    kernel and on the paired kernel (many tokens, features a multiple of 256)."""
+    from cpi_b200.parts.linear import MODE_GEGLU, project
+    g = torch.Generator().manual_seed(T)
+    h = torch.randn(T, H, generator=g).to(dtype).cuda()
+    w = (torch.randn(2 * I, H, generator=g) * H ** -0.5 * 2).to(torch.bfloat16).cuda()
+    out = torch.empty(T, I, dtype=dtype, device="cuda")
+    project(h, w, out, MODE_GEGLU)
+    gu = h.double() @ w.double().T
+    ref = P.gelu_tanh(gu[:, :I]) * gu[:, I:]
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    assert (out.double() - ref).abs().max() < tol * ref.abs().max()
+
+
 # ---- each mixer alone, as a one-layer model --------------------------------------------------------------
 ALONE = {
     "attention_window_sink": V.model([V.attention(4, 2, 24, 40, window=9, rot_dims=12)], 56, 90),
