@@ -33,6 +33,10 @@ configurations that lie inside what that engine computes.
 prompts of 64 to 2,048 tokens, 128 new tokens each.  `--workload long131k`: 12 Scout layers, one prompt of
 131,072 tokens (prefilled in pieces), 256 new tokens.  Both run through `Model.generate` and are timed with
 its wall-clock phases, second of two runs.
+`--workload veredra`: the Veredra design (gated linear attention, windowed attention with a sink, a selective
+state-space layer; gelu-gated feed-forwards; two residual streams) at two layer sizes, six layers each, beside the
+dense Llama4-style decoder at the same sizes: one prefill of 2,048 tokens and decode at batch 8, device-timed, then
+the time of every phase and each phase's fraction of its roofline for both models.
 """
 from __future__ import annotations
 
@@ -594,6 +598,160 @@ def run_cpu_baseline(args) -> dict:
     return out
 
 
+VEREDRA_SIZES = {
+    # width, ff, attention (heads, kv heads, head size, window), gla (heads, key size, value size), mamba2 (heads,
+    # head size, state, groups): two points with the layer shapes of 1-3 B and 7-8 B parameter models
+    "w2048": dict(width=2048, ff=8192, attn=(16, 4, 128, 1024), gla=(8, 128, 256), mamba=(64, 64, 128, 8)),
+    "w4096": dict(width=4096, ff=14336, attn=(32, 8, 128, 2048), gla=(16, 128, 256), mamba=(128, 64, 128, 8)),
+}
+
+
+def veredra_config(sz: dict, vocab: int, reps: int) -> dict:
+    H, G, D, win = sz["attn"]
+    gh, gk, gv = sz["gla"]
+    mh, mv, mn, mg = sz["mamba"]
+    mlp = {"kind": "dense", "ff": sz["ff"]}
+    one = [{"type": "gla", "mixer": {"heads": gh, "dim": gk, "vdim": gv, "tau": 16.0}, "mlp": mlp},
+           {"type": "attention", "mixer": {"heads": H, "kv_heads": G, "dim": D, "vdim": D, "scale": D ** -0.5,
+                                           "rot": {"base": 1e6, "dims": D // 2}, "mask": {"size": win}}, "mlp": mlp},
+           {"type": "mamba2", "mixer": {"heads": mh, "vdim": mv, "state": mn, "groups": mg, "conv": 4,
+                                        "norm_groups": mg}, "mlp": mlp}]
+    return {"architecture": "Veredra", "layers": one * reps, "norm": {"eps": 1e-6}, "streams": 2, "vocab": vocab,
+            "width": sz["width"], "logit_scale": 1.0, "logit_softcap": 30.0}
+
+
+def llama_dense_config(sz: dict, vocab: int, layers: int) -> dict:
+    """The closest model the library already had, at equal sizes: every layer attention (rotary, chunked by the
+    same span as Veredra's window) and a dense SwiGLU feed-forward."""
+    H, G, D, win = sz["attn"]
+    cfg = dict(SCOUT)
+    cfg.update({"num_hidden_layers": layers, "hidden_size": sz["width"], "num_attention_heads": H,
+                "num_key_value_heads": G, "head_dim": D, "intermediate_size": sz["ff"], "intermediate_size_mlp": sz["ff"],
+                "interleave_moe_layer_step": 1 << 20, "vocab_size": vocab, "nope_layer_interval": 0,
+                "attention_chunk_size": win, "attn_temperature_tuning": False})
+    cfg.pop("moe_layers", None)
+    return cfg
+
+
+def run_veredra(args) -> dict:
+    """Prefill and decode of Veredra at two layer sizes beside the dense Llama4-style decoder at equal sizes, with
+    the time of every phase per layer that has it and each phase's share of its roofline (products: flops over the
+    measured bf16 rate in prefill, weight bytes over the measured copy rate in decode; attention: flops / cache
+    bytes; recurrences, norms and stream mixing: bytes)."""
+    import torch
+    from cpi_b200.engine import Engine, StepEntry
+
+    pk = peaks()
+    vocab, reps, T, B = 32000, 2, 2048, 8
+    g = torch.Generator().manual_seed(7)
+    toks = lambda n: torch.randint(0, vocab, (n,), generator=g).tolist()
+    out = {"metric": "tokens/s, Veredra beside the dense decoder at equal layer sizes (bf16, random weights)",
+           "unit": "tokens/s", "dtype": "bf16", "data": "synthetic", "peaks": pk, "points": {}}
+
+    def measure(cfg, n_layers):
+        eng = Engine.from_random(cfg, 0, dtype="bfloat16", max_tokens=(B + 1) * (T + 128), max_seqs=B + 1,
+                                 max_seq_len=T + 128)
+        res = {}
+
+        def prefill():
+            s = eng.acquire_slot()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            eng.step([StepEntry(s, toks(T), [T - 1])])
+            e1.record()
+            torch.cuda.synchronize()
+            eng.release_slot(s)
+            return e0.elapsed_time(e1)
+
+        times = sorted(prefill() for _ in range(6))[:-1]          # the first (slowest) pass warms up
+        res["prefill_ms"] = round(times[len(times) // 2], 3)
+        res["prefill_tok_s"] = round(T / (res["prefill_ms"] / 1e3), 1)
+        slots = [eng.acquire_slot() for _ in range(B)]
+        eng.step([StepEntry(s, toks(T - 64), []) for s in slots])
+        for _ in range(8):
+            eng.step([StepEntry(s, toks(1), [0]) for s in slots])
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(32):
+            eng.step([StepEntry(s, toks(1), [0]) for s in slots])
+        e1.record()
+        torch.cuda.synchronize()
+        res["decode_ms_per_step"] = round(e0.elapsed_time(e1) / 32, 4)
+        res["decode_tok_s"] = round(B / (res["decode_ms_per_step"] / 1e3), 1)
+        res["graphs"] = bool(eng.use_graphs)
+        timer = eng.profile_phases(True)
+        for _ in range(4):
+            eng.step([StepEntry(s, toks(1), [0]) for s in slots])
+        for s in slots:
+            eng.release_slot(s)
+        s = eng.acquire_slot()
+        eng.step([StepEntry(s, toks(T), [T - 1])])
+        eng.release_slot(s)
+        ph = timer.collect()
+        eng.profile_phases(False)
+        res["phases_ms"] = {"prefill": {k: round(v, 4) for k, v in ph.get("prefill", {}).items()},
+                            "decode_per_step": {k: round(v / 4, 4) for k, v in ph.get("decode", {}).items()}}
+        del eng
+        torch.cuda.empty_cache()
+        return res
+
+    for name, sz in VEREDRA_SIZES.items():
+        W, ff = sz["width"], sz["ff"]
+        H, G, D, win = sz["attn"]
+        gh, gk, gv = sz["gla"]
+        mh, mv, mn, mg = sz["mamba"]
+        n_layers = 3 * reps
+        ver = measure(veredra_config(sz, vocab, reps), n_layers)
+        lla = measure(llama_dense_config(sz, vocab, n_layers), n_layers)
+        tf, bw = pk["bf16_tflops"] * 1e12, pk["hbm_gbs"] * 1e9
+        keys = sum(min(t + 1, win) for t in range(T))
+        # per layer that has the phase: what the phase must do at least
+        attn_flops = 4.0 * D * H * keys
+        attn_dec_bytes = B * min(T, win) * G * 2 * D * 2.0
+        mlp_params, qkv_attn, wo_attn = 3.0 * W * ff, (H + 2 * G) * D * W, H * D * W
+        gla_proj = (2 * gh * gk + 2 * gh * gv) * W + 16 * W + 16 * gh * gk
+        inner = mh * mv
+        mamba_proj = (2 * inner + 2 * mg * mn + mh) * W
+        scan_prefill_bytes = {"gla": T * (3 * gh * gk + 2 * gh * gv) * 4.0, "mamba2": T * (2 * mg * mn + 2 * inner + mh) * 4.0}
+        scan_decode_bytes = {"gla": B * gh * gk * gv * 8.0, "mamba2": B * mh * mn * mv * 8.0}
+
+        def frac(ms, flops=0.0, nbytes=0.0):
+            return None if not ms else round(max(flops / tf, nbytes / bw) / (ms / 1e3), 4)
+
+        vp, vd = ver["phases_ms"]["prefill"], ver["phases_ms"]["decode_per_step"]
+        lp, ld = lla["phases_ms"]["prefill"], lla["phases_ms"]["decode_per_step"]
+        roof = {
+            "mlp": {"veredra": {"prefill": frac(vp.get("mlp", 0) / n_layers, 2.0 * T * mlp_params),
+                                "decode": frac(vd.get("mlp", 0) / n_layers, nbytes=2.0 * mlp_params)},
+                    "dense": {"prefill": frac(lp.get("mlp", 0) / n_layers, 2.0 * T * mlp_params),
+                              "decode": frac(ld.get("mlp", 0) / n_layers, nbytes=2.0 * mlp_params)}},
+            "attention": {"veredra": {"prefill": frac(vp.get("attention", 0) / reps, attn_flops),
+                                      "decode": frac(vd.get("attention", 0) / reps, nbytes=attn_dec_bytes)},
+                          "dense": {"prefill": frac(lp.get("attention", 0) / n_layers, attn_flops),
+                                    "decode": frac(ld.get("attention", 0) / n_layers, nbytes=attn_dec_bytes)}},
+            "qkv_and_wo": {"veredra": {"prefill": frac((vp.get("qkv", 0) + vp.get("wo", 0)) / reps,
+                                                       2.0 * T * (qkv_attn + wo_attn + gla_proj + gh * gv * W + mamba_proj + inner * W)),
+                                       "decode": frac((vd.get("qkv", 0) + vd.get("wo", 0)) / reps, nbytes=2.0 * (
+                                           qkv_attn + wo_attn + gla_proj + gh * gv * W + mamba_proj + inner * W))},
+                           "dense": {"prefill": frac((lp.get("qkv", 0) + lp.get("wo", 0)) / n_layers, 2.0 * T * (qkv_attn + wo_attn)),
+                                     "decode": frac((ld.get("qkv", 0) + ld.get("wo", 0)) / n_layers, nbytes=2.0 * (qkv_attn + wo_attn))}},
+            "scan (gla + mamba2, no like kernel)": {"veredra": {
+                "prefill": frac(vp.get("scan", 0) / reps, nbytes=sum(scan_prefill_bytes.values())),
+                "decode": frac(vd.get("scan", 0) / reps, nbytes=sum(scan_decode_bytes.values()))}},
+            "norms_and_residual": {
+                "veredra": {"prefill": frac(vp.get("rmsnorm", 0) / n_layers, nbytes=T * W * (3 * 2 * 2 * 4 + 2 * 4 + 2 * 2.0))},
+                "dense": {"prefill": frac(lp.get("rmsnorm", 0) / n_layers, nbytes=T * W * 2 * (4 + 2.0))}},
+        }
+        out["points"][name] = {"sizes": sz, "layers": n_layers, "prefill_tokens": T, "decode_batch": B,
+                               "decode_context": T - 64, "veredra": ver, "dense": lla, "fraction_of_roofline": roof}
+    big = out["points"]["w4096"]
+    out["value"] = big["veredra"]["decode_tok_s"]
+    out["config"] = {"model": "Veredra, 6 layers (gla, attention, mamba2) x 2, two streams", "global_batch": B,
+                     "seq_len": T, "parallelism": "single GPU", "l2": "weights of a step exceed the L2"}
+    return out
+
+
 def reference_arm_reason() -> str:
     """Why `--impl reference` has nothing to run, as found on this image (one line)."""
     return ("kurulav1/cpi is a CMake C++/CUDA project (no setup.py or pyproject.toml, so pip has nothing to install); "
@@ -613,7 +771,7 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--skip-points", action="store_true")
-    ap.add_argument("--workload", choices=["scout24", "maverick4", "long131k", "contexts", "cpu_baseline"],
+    ap.add_argument("--workload", choices=["scout24", "maverick4", "long131k", "contexts", "cpu_baseline", "veredra"],
                     default="scout24")
     ap.add_argument("--reference-root", default=os.environ.get("CPI_REFERENCE_ROOT"),
                     help="a checkout of kurulav1/cpi (for --workload cpu_baseline)")
@@ -628,6 +786,9 @@ def main() -> int:
         print(json.dumps({"error": "cpi_b200 is a single-GPU library: run with --gpus 1", "n_gpus": args.gpus}))
         return 2
     args.warmup = max(args.warmup, 3)
+    if args.workload == "veredra":
+        print(json.dumps(run_veredra(args)))
+        return 0
     if args.workload == "contexts":
         print(json.dumps(run_contexts(args)))
         return 0

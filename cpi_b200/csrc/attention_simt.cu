@@ -236,7 +236,7 @@ struct QkvPrepParams {
 };
 
 template <typename TI, typename TO>
-__global__ void __launch_bounds__(256) qkv_prepare_kernel(QkvPrepParams p) {
+__global__ void __launch_bounds__(1024) qkv_prepare_kernel(QkvPrepParams p) {
   pdl_launch_dependents();
   extern __shared__ float row_s[];                       // q then k of this token, float32
   __shared__ float scratch[32];
@@ -447,11 +447,13 @@ extern "C" int cpi_qkv_prepare(const void* qkv, int in_dtype, long qkv_stride, c
                   seq_slot, n_heads, n_kv_heads, head_dim, v_dim, write_kv};
   const size_t smem = (size_t)(n_heads + (write_kv ? n_kv_heads : 0)) * head_dim * sizeof(float);
   CPI_REQUIRE(smem <= 200 * 1024, "qkv_prepare: a q and k row of %zu bytes does not fit in shared memory", smem);
+  // with few tokens the blocks are large (a few elements per thread); a prompt has blocks enough
+  const int threads = n_tokens <= 2 * sm_count() ? 1024 : 256;
 #define CPI_PREP(TI, TO)                                                                                       \
   do {                                                                                                         \
     auto kern = qkv_prepare_kernel<TI, TO>;                                                                    \
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
-    cpi::launch_pdl(kern, dim3(n_tokens), dim3(256), smem, stream, p);                                         \
+    cpi::launch_pdl(kern, dim3(n_tokens), dim3(threads), smem, stream, p);                                       \
   } while (0)
   if (in_dtype == kF32 && out_dtype == kF32) CPI_PREP(float, float);
   else if (in_dtype == kF32 && out_dtype == kBF16) CPI_PREP(float, __nv_bfloat16);

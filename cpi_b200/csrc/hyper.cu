@@ -32,7 +32,7 @@ struct HcParams {
 };
 
 template <typename TO>
-__global__ void __launch_bounds__(256) hc_step_kernel(HcParams p) {
+__global__ void __launch_bounds__(1024) hc_step_kernel(HcParams p) {
   pdl_launch_dependents();
   __shared__ float scratch[32];
   __shared__ float coef[HC_MAX_STREAMS * HC_MAX_STREAMS + 2 * HC_MAX_STREAMS];
@@ -52,7 +52,7 @@ __global__ void __launch_bounds__(256) hc_step_kernel(HcParams p) {
   const int t = p.rows ? p.rows[r] : r;
   float* xt = p.x + (size_t)t * W;
   const float* yt = p.y ? p.y + (size_t)t * p.y_stride : nullptr;
-  constexpr int PER = 8;                                   // elements a thread keeps between the two passes
+  constexpr int PER = 4;                                   // elements a thread keeps between the two passes
   float ss = 0.f;
   // write-back of the sublayer before (if any) and the mixture for the next one, at element i
   auto element = [&](int i) -> float {
@@ -84,12 +84,48 @@ __global__ void __launch_bounds__(256) hc_step_kernel(HcParams p) {
     if (p.sum_out) p.sum_out[(size_t)r * W + i] = u;
     return u;
   };
+  // The first PER elements of a thread: every load is issued before the first store (the streams are read and
+  // written through one pointer, so the compiler would otherwise keep each element's loads behind the stores of
+  // the one before: a round trip to memory per element).
   float u_keep[PER];
+  {
+    float xs[PER][HC_MAX_STREAMS], yv[PER];
 #pragma unroll
-  for (int j = 0; j < PER; ++j) {
-    const int i = threadIdx.x + j * blockDim.x;
-    u_keep[j] = i < W ? element(i) : 0.f;
-    ss = fmaf(u_keep[j], u_keep[j], ss);
+    for (int j = 0; j < PER; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+#pragma unroll
+      for (int s = 0; s < HC_MAX_STREAMS; ++s) xs[j][s] = (s < S && i < W) ? xt[(size_t)s * p.stream_stride + i] : 0.f;
+      yv[j] = (yt && i < W) ? yt[i] : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      float u = 0.f;
+      if (i < W) {
+        if (yt) {
+          float nx[HC_MAX_STREAMS];
+#pragma unroll
+          for (int to = 0; to < HC_MAX_STREAMS; ++to) {
+            if (to < S) {
+              float acc = 0.f;
+#pragma unroll
+              for (int s = 0; s < HC_MAX_STREAMS; ++s)
+                if (s < S) acc = fmaf(mix_s[s * S + to], xs[j][s], acc);
+              nx[to] = fmaf(write_s[to], yv[j], acc);
+            }
+          }
+#pragma unroll
+          for (int s = 0; s < HC_MAX_STREAMS; ++s)
+            if (s < S) { xs[j][s] = nx[s]; xt[(size_t)s * p.stream_stride + i] = nx[s]; }
+        }
+#pragma unroll
+        for (int s = 0; s < HC_MAX_STREAMS; ++s)
+          if (s < S) u = fmaf(read_s[s], xs[j][s], u);
+        if (p.sum_out) p.sum_out[(size_t)r * W + i] = u;
+      }
+      u_keep[j] = u;
+      ss = fmaf(u, u, ss);
+    }
   }
   for (int i = threadIdx.x + PER * blockDim.x; i < W; i += blockDim.x) {     // a very wide row
     const float u = element(i);
@@ -134,7 +170,9 @@ extern "C" int cpi_hc_step(float* x, long stream_stride, int n_streams, int n_ro
   CPI_REQUIRE(!y || (mix && write), "hyper-connections: a write-back needs its mixing matrix and write weights");
   HcParams p{x, stream_stride, n_streams, width, y, y_stride, mix, write, read, rows,
              norm_w, norm_w_dtype, norm_offset, eps, h_out, h_stride, sum_out};
-  const int threads = width <= 256 ? 64 : (width <= 1024 ? 128 : 256);
+  // a thread takes four elements at most in one round of loads: wide rows get large blocks
+  int threads = (width + 3) / 4;
+  threads = threads <= 64 ? 64 : (threads <= 128 ? 128 : (threads <= 256 ? 256 : (threads <= 512 ? 512 : 1024)));
   CPI_DISPATCH_DTYPE(h_dtype, TO, cpi::launch_pdl(hc_step_kernel<TO>, n_rows, threads, 0, stream, p));
   return check_launch("hc_step");
 }

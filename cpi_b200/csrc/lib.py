@@ -425,7 +425,8 @@ def linear_scan(k, q, v, state, out, batch, *, n_heads, heads_per_group, n_rows,
           _p(z), c_long(0 if z is None else z.stride(0)), _p(z_bias), c_float(1.0 / float(tau)),
           _p(dt), c_long(0 if dt is None else dt.stride(0)), _p(dt_bias), _p(a_log), _p(skip), c_int(dtype_code(sd)),
           c_float(q_scale), _p(state), _p(out), c_long(out.stride(0)), _p(batch.seq_slot), _p(batch.seq_tok0),
-          _p(batch.seq_new), c_int(batch.n_seqs), c_int(n_heads), c_int(heads_per_group), c_int(n_rows), c_int(n_cols),
+          _p(batch.seq_new), c_int(batch.n_seqs), c_int(getattr(batch, "max_new", 1 << 20)), c_int(n_heads),
+          c_int(heads_per_group), c_int(n_rows), c_int(n_cols),
           _stream())
 
 

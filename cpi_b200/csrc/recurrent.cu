@@ -92,39 +92,61 @@ struct ScanParams {
   const int* seq_slot; const int* seq_tok0; const int* seq_new;
   int n_heads, heads_per_group, n_rows, n_cols;      // H, H / groups, N, Dv
   int chunk;                             // tokens staged in shared memory at a time
+  int vec16;                             // the rows of k, q and z start on 16-byte boundaries and N is a multiple of 4
 };
 
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
 __device__ __forceinline__ float log_sigmoid_f(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
+__device__ __forceinline__ void cp_async4(float* dst_smem, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst_smem))), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async16(float* dst_smem, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst_smem))), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 // Threads of a warp: lane = kk * PVW + pp with KS lanes (kk) sharing a column and PVW = 32 / KS columns (pp) per
-// warp.  Lane kk owns the state rows kk * NPT .. kk * NPT + NPT - 1 of its column in registers.  A chunk of
-// tokens is staged in shared memory: per token the rows' k, q and decay, each lane group's NPT values followed
-// by four words of padding, so that the 16-byte reads of different kk fall into different banks.
+// warp.  Lane kk owns the state rows kk * NPT .. kk * NPT + NPT - 1 of its column in registers.  Tokens come
+// through shared memory a chunk at a time, in two buffers: while one chunk is computed the next one's rows (k, q,
+// the decays before their transform, the block's columns of v, the raw step sizes) are on their way as
+// asynchronous copies, 16 bytes each where the rows allow it.  Once a chunk has landed, one pass turns what was
+// copied into what the recurrence needs (q scaled; a = sigmoid(z + b)^(1/tau), or the step size and the head's
+// decay).  Per token the rows' k, q and a lie as each lane group's NPT values followed by four words of padding,
+// so that the 16-byte reads of different kk fall into different banks.
 template <int NPT, int KS, bool ROW_DECAY>
-__global__ void __launch_bounds__(128) linear_scan_kernel(ScanParams p) {
+__global__ void __launch_bounds__(256) linear_scan_kernel(ScanParams p) {
   pdl_launch_dependents();
   extern __shared__ __align__(16) float smem[];
-  constexpr int PVW = 32 / KS, ROWP = KS * (NPT + 4);
+  constexpr int PVW = 32 / KS, ROWP = KS * (NPT + 4), NVEC = ROW_DECAY ? 3 : 2;
   const int nwarps = blockDim.x >> 5, pvb = nwarps * PVW;
   const int s = blockIdx.x, h = blockIdx.y;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, kk = lane / PVW, pp = lane % PVW;
-  const int col = blockIdx.z * pvb + warp * PVW + pp;
+  const int col0 = blockIdx.z * pvb, col = col0 + warp * PVW + pp;
   const int N = p.n_rows, Dv = p.n_cols, H = p.n_heads, g = h / p.heads_per_group;
   const int chunk = p.chunk;
-  float* k_s = smem;                                         // [chunk][ROWP]
-  float* q_s = k_s + (size_t)chunk * ROWP;
-  float* d_s = q_s + (size_t)chunk * ROWP;                   // row decays (row flavour only)
-  float* v_s = d_s + (ROW_DECAY ? (size_t)chunk * ROWP : 0); // [chunk][pvb]
-  float* a_s = v_s + (size_t)chunk * pvb;                    // [chunk] head decay, [chunk] step size (head flavour)
-  float* dt_s = a_s + chunk;
+  const int per_buf = (chunk * (NVEC * ROWP + pvb + 2) + 3) & ~3;
+  float* bias_s = smem + 2 * per_buf;                        // [KS * NPT] the decays' bias (row flavour)
+  auto k_of = [&](float* b) { return b; };
+  auto q_of = [&](float* b) { return b + (size_t)chunk * ROWP; };
+  auto d_of = [&](float* b) { return b + (size_t)2 * chunk * ROWP; };
+  auto v_of = [&](float* b) { return b + (size_t)NVEC * chunk * ROWP; };
+  auto dt_of = [&](float* b) { return b + (size_t)NVEC * chunk * ROWP + (size_t)chunk * pvb; };
+  auto a_of = [&](float* b) { return dt_of(b) + chunk; };
 
+  // what no kernel writes comes before the wait: the head's constants, the bias; the buffers start as zeros
+  // (rows past the state's size and columns past the head's are never copied into and stay zero)
   float head_a = 0.f, head_dtb = 0.f, head_skip = 0.f;
   if (!ROW_DECAY) {
     head_a = -expf(load_any(p.a_log, p.small_dtype, h));
     head_dtb = p.dt_bias ? load_any(p.dt_bias, p.small_dtype, h) : 0.f;
   }
   if (p.skip) head_skip = load_any(p.skip, p.small_dtype, h);
+  for (int i = tid; i < 2 * per_buf; i += blockDim.x) smem[i] = 0.f;
+  if (ROW_DECAY)
+    for (int n = tid; n < KS * NPT; n += blockDim.x)
+      bias_s[n] = (n < N && p.z_bias) ? load_any(p.z_bias, p.small_dtype, (size_t)h * N + n) : 0.f;
   pdl_wait();
   const int n_tok = p.seq_new[s], tok0 = p.seq_tok0[s];
   const bool live = col < Dv;
@@ -135,62 +157,103 @@ __global__ void __launch_bounds__(128) linear_scan_kernel(ScanParams p) {
     const int n = kk * NPT + i;
     S[i] = (live && n < N) ? st[(size_t)n * Dv] : 0.f;
   }
-  for (int c0 = 0; c0 < n_tok; c0 += chunk) {
+  __syncthreads();                                           // the zeros are in place before the first copies land
+
+  auto issue = [&](int c0, float* b) {
     const int nc = min(chunk, n_tok - c0);
-    __syncthreads();                                         // the chunk before has been used
-    for (int e = tid; e < nc * KS * NPT; e += blockDim.x) {
-      const int j = e / (KS * NPT), n = e % (KS * NPT);
-      const int at = j * ROWP + (n / NPT) * (NPT + 4) + n % NPT;
-      const size_t t = (size_t)(tok0 + c0 + j);
-      float kv = 0.f, qv = 0.f, dv = 0.f;
-      if (n < N) {
-        kv = p.k[t * p.k_stride + (size_t)g * N + n];
-        qv = p.q[t * p.q_stride + (size_t)g * N + n] * p.q_scale;
-        if (ROW_DECAY) {
-          float zz = p.z[t * p.z_stride + (size_t)h * N + n];
-          if (p.z_bias) zz += load_any(p.z_bias, p.small_dtype, (size_t)h * N + n);
-          dv = expf(log_sigmoid_f(zz) * p.inv_tau);
-        }
+    float *ks = k_of(b), *qs = q_of(b), *ds = d_of(b);
+    if (p.vec16) {
+      constexpr int G4 = KS * NPT / 4;
+      for (int e = tid; e < nc * G4; e += blockDim.x) {
+        const int j = e / G4, n = (e % G4) * 4;
+        if (n >= N) continue;
+        const int at = j * ROWP + (n / NPT) * (NPT + 4) + n % NPT;
+        const size_t t = (size_t)(tok0 + c0 + j);
+        cp_async16(ks + at, p.k + t * p.k_stride + (size_t)g * N + n);
+        cp_async16(qs + at, p.q + t * p.q_stride + (size_t)g * N + n);
+        if (ROW_DECAY) cp_async16(ds + at, p.z + t * p.z_stride + (size_t)h * N + n);
       }
-      k_s[at] = kv; q_s[at] = qv;
-      if (ROW_DECAY) d_s[at] = dv;
+    } else {
+      for (int e = tid; e < nc * KS * NPT; e += blockDim.x) {
+        const int j = e / (KS * NPT), n = e % (KS * NPT);
+        if (n >= N) continue;
+        const int at = j * ROWP + (n / NPT) * (NPT + 4) + n % NPT;
+        const size_t t = (size_t)(tok0 + c0 + j);
+        cp_async4(ks + at, p.k + t * p.k_stride + (size_t)g * N + n);
+        cp_async4(qs + at, p.q + t * p.q_stride + (size_t)g * N + n);
+        if (ROW_DECAY) cp_async4(ds + at, p.z + t * p.z_stride + (size_t)h * N + n);
+      }
     }
+    float* vs = v_of(b);
     for (int e = tid; e < nc * pvb; e += blockDim.x) {
-      const int j = e / pvb, c = blockIdx.z * pvb + e % pvb;
-      v_s[e] = c < Dv ? p.v[(size_t)(tok0 + c0 + j) * p.v_stride + (size_t)h * Dv + c] : 0.f;
+      const int j = e / pvb, c = col0 + e % pvb;
+      if (c < Dv) cp_async4(vs + e, p.v + (size_t)(tok0 + c0 + j) * p.v_stride + (size_t)h * Dv + c);
+    }
+    if (!ROW_DECAY) {
+      float* dts = dt_of(b);
+      for (int j = tid; j < nc; j += blockDim.x) cp_async4(dts + j, p.dt + (size_t)(tok0 + c0 + j) * p.dt_stride + h);
+    }
+  };
+
+  if (n_tok > 0) issue(0, smem);
+  cp_async_commit();
+  int which = 0;
+  for (int c0 = 0; c0 < n_tok; c0 += chunk, which ^= 1) {
+    float* b = smem + which * per_buf;
+    const int nc = min(chunk, n_tok - c0);
+    if (c0 + chunk < n_tok) issue(c0 + chunk, smem + (which ^ 1) * per_buf);
+    cp_async_commit();
+    cp_async_wait<1>();                                      // this chunk's copies (the group before the newest) are done
+    __syncthreads();
+    // what was copied becomes what the recurrence needs
+    float *ks = k_of(b), *qs = q_of(b), *ds = d_of(b), *vs = v_of(b), *dts = dt_of(b), *as = a_of(b);
+    if (ROW_DECAY || p.q_scale != 1.0f) {
+      for (int e = tid; e < nc * KS * NPT; e += blockDim.x) {
+        const int j = e / (KS * NPT), n = e % (KS * NPT);
+        if (n >= N) continue;
+        const int at = j * ROWP + (n / NPT) * (NPT + 4) + n % NPT;
+        qs[at] *= p.q_scale;
+        if (ROW_DECAY) ds[at] = expf(log_sigmoid_f(ds[at] + bias_s[n]) * p.inv_tau);
+      }
     }
     if (!ROW_DECAY) {
       for (int j = tid; j < nc; j += blockDim.x) {
-        const float dt = softplus_f(p.dt[(size_t)(tok0 + c0 + j) * p.dt_stride + h] + head_dtb);
-        dt_s[j] = dt;
-        a_s[j] = expf(head_a * dt);
+        const float dt = softplus_f(dts[j] + head_dtb);
+        dts[j] = dt;
+        as[j] = expf(head_a * dt);
       }
     }
     __syncthreads();
+    // (unrolled: the state's chain from token to token is two instructions long; the sum over a column's lanes and
+    // the store of a token overlap the tokens after it)
+#pragma unroll 4
     for (int j = 0; j < nc; ++j) {
-      const float4* k4 = reinterpret_cast<const float4*>(k_s + j * ROWP + kk * (NPT + 4));
-      const float4* q4 = reinterpret_cast<const float4*>(q_s + j * ROWP + kk * (NPT + 4));
-      const float4* d4 = reinterpret_cast<const float4*>(d_s + j * ROWP + kk * (NPT + 4));
-      const float v_raw = v_s[j * pvb + warp * PVW + pp];
+      const float4* k4 = reinterpret_cast<const float4*>(ks + j * ROWP + kk * (NPT + 4));
+      const float4* q4 = reinterpret_cast<const float4*>(qs + j * ROWP + kk * (NPT + 4));
+      const float4* d4 = reinterpret_cast<const float4*>(ds + j * ROWP + kk * (NPT + 4));
+      const float v_raw = vs[j * pvb + warp * PVW + pp];
       float vv = v_raw, a = 0.f;
-      if (!ROW_DECAY) { vv = v_raw * dt_s[j]; a = a_s[j]; }
-      float o = 0.f;
+      if (!ROW_DECAY) { vv = v_raw * dts[j]; a = as[j]; }
+      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;          // four chains: the sum over a lane's rows is not one long chain
 #pragma unroll
       for (int i4 = 0; i4 < NPT / 4; ++i4) {
         const float4 kq = k4[i4], qq = q4[i4];
         float4 dd = make_float4(a, a, a, a);
         if (ROW_DECAY) dd = d4[i4];
-        S[4 * i4 + 0] = fmaf(kq.x, vv, dd.x * S[4 * i4 + 0]); o = fmaf(S[4 * i4 + 0], qq.x, o);
-        S[4 * i4 + 1] = fmaf(kq.y, vv, dd.y * S[4 * i4 + 1]); o = fmaf(S[4 * i4 + 1], qq.y, o);
-        S[4 * i4 + 2] = fmaf(kq.z, vv, dd.z * S[4 * i4 + 2]); o = fmaf(S[4 * i4 + 2], qq.z, o);
-        S[4 * i4 + 3] = fmaf(kq.w, vv, dd.w * S[4 * i4 + 3]); o = fmaf(S[4 * i4 + 3], qq.w, o);
+        S[4 * i4 + 0] = fmaf(kq.x, vv, dd.x * S[4 * i4 + 0]); o0 = fmaf(S[4 * i4 + 0], qq.x, o0);
+        S[4 * i4 + 1] = fmaf(kq.y, vv, dd.y * S[4 * i4 + 1]); o1 = fmaf(S[4 * i4 + 1], qq.y, o1);
+        S[4 * i4 + 2] = fmaf(kq.z, vv, dd.z * S[4 * i4 + 2]); o2 = fmaf(S[4 * i4 + 2], qq.z, o2);
+        S[4 * i4 + 3] = fmaf(kq.w, vv, dd.w * S[4 * i4 + 3]); o3 = fmaf(S[4 * i4 + 3], qq.w, o3);
       }
+      float o = (o0 + o1) + (o2 + o3);
 #pragma unroll
       for (int off = PVW; off < 32; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
       if (kk == 0 && live)
         p.out[(size_t)(tok0 + c0 + j) * p.out_stride + (size_t)h * Dv + col] = fmaf(head_skip, v_raw, o);
     }
+    __syncthreads();                                         // the buffer may be copied into again
   }
+  cp_async_wait<0>();
 #pragma unroll
   for (int i = 0; i < NPT; ++i) {
     const int n = kk * NPT + i;
@@ -235,43 +298,62 @@ __global__ void __launch_bounds__(128) gated_norm_kernel(GatedNormParams p) {
 }
 
 template <int NPT, int KS, bool ROW>
-static int launch_scan(const ScanParams& p0, int n_seqs, cudaStream_t stream) {
+static int launch_scan(const ScanParams& p0, int n_seqs, int max_new, int max_warps, cudaStream_t stream) {
   ScanParams p = p0;
   constexpr int PVW = 32 / KS, ROWP = KS * (NPT + 4);
   int nwarps = (p.n_cols + PVW - 1) / PVW;
-  if (nwarps > 2) nwarps = 2;
+  if (nwarps > max_warps) nwarps = max_warps;
   const int pvb = nwarps * PVW;
   const int per_token = (ROW ? 3 : 2) * ROWP + pvb + 2;
-  int chunk = (40 * 1024 / 4) / per_token;
-  if (chunk > 32) chunk = 32;
+  int chunk = (36 * 1024 / 4) / per_token;                   // two buffers of this many tokens: three blocks share an SM
+  if (chunk > 16) chunk = 16;
+  if (chunk > max_new) chunk = max_new;                      // a decode step stages one token: small blocks, all resident
   if (chunk < 1) chunk = 1;
   p.chunk = chunk;
-  const size_t smem = (size_t)chunk * per_token * sizeof(float);
+  const int per_buf = (chunk * per_token + 3) & ~3;
+  const size_t smem = ((size_t)2 * per_buf + KS * NPT) * sizeof(float);
+  auto aligned = [](const float* q, long stride) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0 && stride % 4 == 0; };
+  p.vec16 = p.n_rows % 4 == 0 && aligned(p.k, p.k_stride) && aligned(p.q, p.q_stride) && (!ROW || aligned(p.z, p.z_stride));
   auto kern = linear_scan_kernel<NPT, KS, ROW>;
-  if (smem > 48 * 1024) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+  static bool attr_set = false;                              // per instantiation
+  if (smem > 48 * 1024 && !attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) {
       set_error("linear_scan: %zu bytes of shared memory were refused", smem);
       return 1;
     }
+    attr_set = true;
   }
   dim3 grid(n_seqs, p.n_heads, (p.n_cols + pvb - 1) / pvb);
   cpi::launch_pdl(kern, grid, dim3(32 * nwarps), smem, stream, p);
   return check_launch("linear_scan");
 }
 
+// Two shapes of block.  Narrow: four lanes share a column, each with a quarter of the rows in registers, two warps
+// (16 columns) per block: the most columns per byte of staging, for steps with many sequences.  Wide: sixteen
+// lanes share a column, eight warps (16 columns) per block: four times the threads and a quarter of the
+// instructions per thread and token, for a prompt of one or a few sequences, where the token-by-token chain of one
+// (sequence, head) is what the step waits for and most of the GPU would idle.
 template <bool ROW>
-static int dispatch_scan(const ScanParams& p, int n_seqs, cudaStream_t stream) {
+static int dispatch_scan(const ScanParams& p, int n_seqs, int max_new, cudaStream_t stream) {
   const int N = p.n_rows;
-  if (N <= 16) return launch_scan<4, 4, ROW>(p, n_seqs, stream);
-  if (N <= 32) return launch_scan<8, 4, ROW>(p, n_seqs, stream);
-  if (N <= 48) return launch_scan<12, 4, ROW>(p, n_seqs, stream);
-  if (N <= 64) return launch_scan<16, 4, ROW>(p, n_seqs, stream);
-  if (N <= 96) return launch_scan<24, 4, ROW>(p, n_seqs, stream);
-  if (N <= 128) return launch_scan<32, 4, ROW>(p, n_seqs, stream);
-  if (N <= 192) return launch_scan<48, 4, ROW>(p, n_seqs, stream);
-  if (N <= 256) return launch_scan<64, 4, ROW>(p, n_seqs, stream);
-  if (N <= 512) return launch_scan<64, 8, ROW>(p, n_seqs, stream);
-  if (N <= 1024) return launch_scan<64, 16, ROW>(p, n_seqs, stream);
+  const long narrow_blocks = (long)n_seqs * p.n_heads * ((p.n_cols + 15) / 16);
+  const bool wide = max_new > 16 && narrow_blocks < 4l * sm_count() && N > 16 && N <= 256;
+  if (wide) {
+    if (N <= 64) return launch_scan<4, 16, ROW>(p, n_seqs, max_new, 8, stream);
+    if (N <= 128) return launch_scan<8, 16, ROW>(p, n_seqs, max_new, 8, stream);
+    if (N <= 192) return launch_scan<12, 16, ROW>(p, n_seqs, max_new, 8, stream);
+    return launch_scan<16, 16, ROW>(p, n_seqs, max_new, 8, stream);
+  }
+  if (N <= 16) return launch_scan<4, 4, ROW>(p, n_seqs, max_new, 2, stream);
+  if (N <= 32) return launch_scan<8, 4, ROW>(p, n_seqs, max_new, 2, stream);
+  if (N <= 48) return launch_scan<12, 4, ROW>(p, n_seqs, max_new, 2, stream);
+  if (N <= 64) return launch_scan<16, 4, ROW>(p, n_seqs, max_new, 2, stream);
+  if (N <= 96) return launch_scan<24, 4, ROW>(p, n_seqs, max_new, 2, stream);
+  if (N <= 128) return launch_scan<32, 4, ROW>(p, n_seqs, max_new, 2, stream);
+  if (N <= 192) return launch_scan<48, 4, ROW>(p, n_seqs, max_new, 2, stream);
+  if (N <= 256) return launch_scan<64, 4, ROW>(p, n_seqs, max_new, 2, stream);
+  if (N <= 512) return launch_scan<64, 8, ROW>(p, n_seqs, max_new, 2, stream);
+  if (N <= 1024) return launch_scan<64, 16, ROW>(p, n_seqs, max_new, 2, stream);
   set_error("linear_scan: a state of %d rows per head is not supported (up to 1024)", N);
   return 1;
 }
@@ -305,7 +387,7 @@ extern "C" int cpi_linear_scan(const float* k, long k_stride, const float* q, lo
                                const float* dt, long dt_stride, const void* dt_bias, const void* a_log,
                                const void* skip, int small_dtype, float q_scale, float* state, float* out,
                                long out_stride, const int* seq_slot, const int* seq_tok0, const int* seq_new,
-                               int n_seqs, int n_heads, int heads_per_group, int n_rows, int n_cols,
+                               int n_seqs, int max_new, int n_heads, int heads_per_group, int n_rows, int n_cols,
                                cudaStream_t stream) {
   if (n_seqs == 0) return 0;
   CPI_REQUIRE((z != nullptr) != (dt != nullptr), "linear_scan: give row decays or step sizes, one of the two");
@@ -316,7 +398,8 @@ extern "C" int cpi_linear_scan(const float* k, long k_stride, const float* q, lo
   ScanParams p{k, k_stride, q, q_stride, v, v_stride, z, z_stride, z_bias, inv_tau, dt, dt_stride, dt_bias, a_log,
                skip, small_dtype, q_scale, state, out, out_stride, seq_slot, seq_tok0, seq_new,
                n_heads, heads_per_group, n_rows, n_cols, 0};
-  return z ? dispatch_scan<true>(p, n_seqs, stream) : dispatch_scan<false>(p, n_seqs, stream);
+  if (max_new < 1) max_new = 1;
+  return z ? dispatch_scan<true>(p, n_seqs, max_new, stream) : dispatch_scan<false>(p, n_seqs, max_new, stream);
 }
 
 extern "C" int cpi_gated_norm(const float* y, long y_stride, const float* gate, long gate_stride, const void* w,

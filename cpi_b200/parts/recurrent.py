@@ -94,15 +94,16 @@ class Mamba2Mixer(Mixer):
         with phase("qkv"):
             project(h, self.w_in, proj)
         xbc = self.ws.get("mamba_xbc", (T, self.channels), f32)
-        with phase("kv_store"):
+        with phase("conv"):
             K.causal_conv(proj[:, inner:inner + self.channels], self.w_conv, self.b_conv, cache.state("conv"), xbc,
                           batch, silu=True)
         y = self.ws.get("mamba_y", (T, inner), f32)
-        with phase("attention"):
+        with phase("scan"):
             K.linear_scan(xbc[:, inner:inner + gn], xbc[:, inner + gn:], xbc[:, :inner], cache.state("ssm"), y, batch,
                           n_heads=self.nh, heads_per_group=self.nh // self.groups, n_rows=self.n, n_cols=self.dv,
                           dt=proj[:, inner + self.channels:], dt_bias=self.dt_bias, a_log=self.a_log,
                           skip=self.d_skip)
+        with phase("gated_norm"):
             g = self.ws.get("mamba_gated", (T, inner), h.dtype)
             K.gated_norm(y, proj[:, :inner], self.w_norm, g, parts=self.norm_groups, gate_first=True, eps=self.eps)
         with phase("wo"):
@@ -161,10 +162,11 @@ class GLAMixer(Mixer):
             project(h, self.w_a1, low)
             project(low, self.w_a2, z)
         o = self.ws.get("gla_o", (T, nv), f32)
-        with phase("attention"):
+        with phase("scan"):
             K.linear_scan(proj[:, nk:2 * nk], proj[:, :nk], proj[:, 2 * nk:2 * nk + nv], cache.state("s"), o, batch,
                           n_heads=self.nh, heads_per_group=1, n_rows=self.dk, n_cols=self.dv, z=z, z_bias=self.b_a2,
                           tau=self.tau, q_scale=self.dk ** -0.5)
+        with phase("gated_norm"):
             g = self.ws.get("gla_gated", (T, nv), h.dtype)
             K.gated_norm(o, proj[:, 2 * nk + nv:], self.w_norm, g, parts=self.nh, gate_first=False, eps=self.eps)
         with phase("wo"):
