@@ -115,15 +115,16 @@ template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile(
 // copied into what the recurrence needs (q scaled; a = sigmoid(z + b)^(1/tau), or the step size and the head's
 // decay).  Per token the rows' k, q and a lie as each lane group's NPT values followed by four words of padding,
 // so that the 16-byte reads of different kk fall into different banks.
-template <int NPT, int KS, bool ROW_DECAY>
+template <int NPT, int KS, bool ROW_DECAY, int CPT>
 __global__ void __launch_bounds__(256) linear_scan_kernel(ScanParams p) {
   pdl_launch_dependents();
   extern __shared__ __align__(16) float smem[];
   constexpr int PVW = 32 / KS, ROWP = KS * (NPT + 4), NVEC = ROW_DECAY ? 3 : 2;
-  const int nwarps = blockDim.x >> 5, pvb = nwarps * PVW;
+  const int nwarps = blockDim.x >> 5, pvb = nwarps * PVW * CPT;
   const int s = blockIdx.x, h = blockIdx.y;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, kk = lane / PVW, pp = lane % PVW;
-  const int col0 = blockIdx.z * pvb, col = col0 + warp * PVW + pp;
+  const int lcol = (warp * PVW + pp) * CPT;                  // this thread's first column within the block's slice
+  const int col0 = blockIdx.z * pvb, col = col0 + lcol;
   const int N = p.n_rows, Dv = p.n_cols, H = p.n_heads, g = h / p.heads_per_group;
   const int chunk = p.chunk;
   const int per_buf = (chunk * (NVEC * ROWP + pvb + 2) + 3) & ~3;
@@ -149,13 +150,13 @@ __global__ void __launch_bounds__(256) linear_scan_kernel(ScanParams p) {
       bias_s[n] = (n < N && p.z_bias) ? load_any(p.z_bias, p.small_dtype, (size_t)h * N + n) : 0.f;
   pdl_wait();
   const int n_tok = p.seq_new[s], tok0 = p.seq_tok0[s];
-  const bool live = col < Dv;
   float* st = p.state + (((size_t)p.seq_slot[s] * H + h) * N) * Dv + col;
-  float S[NPT];
+  float S[NPT][CPT];                                         // rows kk * NPT .., columns col .. col + CPT - 1
 #pragma unroll
   for (int i = 0; i < NPT; ++i) {
     const int n = kk * NPT + i;
-    S[i] = (live && n < N) ? st[(size_t)n * Dv] : 0.f;
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) S[i][c] = (col + c < Dv && n < N) ? st[(size_t)n * Dv + c] : 0.f;
   }
   __syncthreads();                                           // the zeros are in place before the first copies land
 
@@ -224,32 +225,39 @@ __global__ void __launch_bounds__(256) linear_scan_kernel(ScanParams p) {
       }
     }
     __syncthreads();
-    // (unrolled: the state's chain from token to token is two instructions long; the sum over a column's lanes and
-    // the store of a token overlap the tokens after it)
-#pragma unroll 4
+#pragma unroll 1
     for (int j = 0; j < nc; ++j) {
       const float4* k4 = reinterpret_cast<const float4*>(ks + j * ROWP + kk * (NPT + 4));
       const float4* q4 = reinterpret_cast<const float4*>(qs + j * ROWP + kk * (NPT + 4));
       const float4* d4 = reinterpret_cast<const float4*>(ds + j * ROWP + kk * (NPT + 4));
-      const float v_raw = vs[j * pvb + warp * PVW + pp];
-      float vv = v_raw, a = 0.f;
-      if (!ROW_DECAY) { vv = v_raw * dts[j]; a = as[j]; }
-      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;          // four chains: the sum over a lane's rows is not one long chain
+      float v_raw[CPT], vv[CPT], o[CPT];
+      float a = 0.f, dtj = 1.f;
+      if (!ROW_DECAY) { dtj = dts[j]; a = as[j]; }
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) { v_raw[c] = vs[j * pvb + lcol + c]; vv[c] = v_raw[c] * dtj; o[c] = 0.f; }
+      // a thread's rows times its columns: k, q and the decay of a row are read once for all its columns
 #pragma unroll
       for (int i4 = 0; i4 < NPT / 4; ++i4) {
         const float4 kq = k4[i4], qq = q4[i4];
         float4 dd = make_float4(a, a, a, a);
         if (ROW_DECAY) dd = d4[i4];
-        S[4 * i4 + 0] = fmaf(kq.x, vv, dd.x * S[4 * i4 + 0]); o0 = fmaf(S[4 * i4 + 0], qq.x, o0);
-        S[4 * i4 + 1] = fmaf(kq.y, vv, dd.y * S[4 * i4 + 1]); o1 = fmaf(S[4 * i4 + 1], qq.y, o1);
-        S[4 * i4 + 2] = fmaf(kq.z, vv, dd.z * S[4 * i4 + 2]); o2 = fmaf(S[4 * i4 + 2], qq.z, o2);
-        S[4 * i4 + 3] = fmaf(kq.w, vv, dd.w * S[4 * i4 + 3]); o3 = fmaf(S[4 * i4 + 3], qq.w, o3);
-      }
-      float o = (o0 + o1) + (o2 + o3);
+        const float kr[4] = {kq.x, kq.y, kq.z, kq.w}, qr[4] = {qq.x, qq.y, qq.z, qq.w}, dr[4] = {dd.x, dd.y, dd.z, dd.w};
 #pragma unroll
-      for (int off = PVW; off < 32; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
-      if (kk == 0 && live)
-        p.out[(size_t)(tok0 + c0 + j) * p.out_stride + (size_t)h * Dv + col] = fmaf(head_skip, v_raw, o);
+        for (int r = 0; r < 4; ++r) {
+#pragma unroll
+          for (int c = 0; c < CPT; ++c) {
+            S[4 * i4 + r][c] = fmaf(kr[r], vv[c], dr[r] * S[4 * i4 + r][c]);
+            o[c] = fmaf(S[4 * i4 + r][c], qr[r], o[c]);
+          }
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) {
+#pragma unroll
+        for (int off = PVW; off < 32; off <<= 1) o[c] += __shfl_xor_sync(0xffffffffu, o[c], off);
+        if (kk == 0 && col + c < Dv)
+          p.out[(size_t)(tok0 + c0 + j) * p.out_stride + (size_t)h * Dv + col + c] = fmaf(head_skip, v_raw[c], o[c]);
+      }
     }
     __syncthreads();                                         // the buffer may be copied into again
   }
@@ -257,7 +265,9 @@ __global__ void __launch_bounds__(256) linear_scan_kernel(ScanParams p) {
 #pragma unroll
   for (int i = 0; i < NPT; ++i) {
     const int n = kk * NPT + i;
-    if (live && n < N) st[(size_t)n * Dv] = S[i];
+#pragma unroll
+    for (int c = 0; c < CPT; ++c)
+      if (col + c < Dv && n < N) st[(size_t)n * Dv + c] = S[i][c];
   }
 }
 
@@ -297,13 +307,13 @@ __global__ void __launch_bounds__(128) gated_norm_kernel(GatedNormParams p) {
   }
 }
 
-template <int NPT, int KS, bool ROW>
+template <int NPT, int KS, bool ROW, int CPT = 1>
 static int launch_scan(const ScanParams& p0, int n_seqs, int max_new, int max_warps, cudaStream_t stream) {
   ScanParams p = p0;
   constexpr int PVW = 32 / KS, ROWP = KS * (NPT + 4);
-  int nwarps = (p.n_cols + PVW - 1) / PVW;
+  int nwarps = (p.n_cols + PVW * CPT - 1) / (PVW * CPT);
   if (nwarps > max_warps) nwarps = max_warps;
-  const int pvb = nwarps * PVW;
+  const int pvb = nwarps * PVW * CPT;
   const int per_token = (ROW ? 3 : 2) * ROWP + pvb + 2;
   int chunk = (36 * 1024 / 4) / per_token;                   // two buffers of this many tokens: three blocks share an SM
   if (chunk > 16) chunk = 16;
@@ -314,7 +324,7 @@ static int launch_scan(const ScanParams& p0, int n_seqs, int max_new, int max_wa
   const size_t smem = ((size_t)2 * per_buf + KS * NPT) * sizeof(float);
   auto aligned = [](const float* q, long stride) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0 && stride % 4 == 0; };
   p.vec16 = p.n_rows % 4 == 0 && aligned(p.k, p.k_stride) && aligned(p.q, p.q_stride) && (!ROW || aligned(p.z, p.z_stride));
-  auto kern = linear_scan_kernel<NPT, KS, ROW>;
+  auto kern = linear_scan_kernel<NPT, KS, ROW, CPT>;
   static bool attr_set = false;                              // per instantiation
   if (smem > 48 * 1024 && !attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) {
@@ -337,8 +347,11 @@ template <bool ROW>
 static int dispatch_scan(const ScanParams& p, int n_seqs, int max_new, cudaStream_t stream) {
   const int N = p.n_rows;
   const long narrow_blocks = (long)n_seqs * p.n_heads * ((p.n_cols + 15) / 16);
-  const bool wide = max_new > 16 && narrow_blocks < 4l * sm_count() && N > 16 && N <= 256;
+  const bool wide = max_new > 16 && narrow_blocks < 8l * sm_count() && N > 16 && N <= 256;
   if (wide) {
+    // (one column per thread: a register tile of four columns per thread, which reads a row's k, q and decay once
+    // for four columns, was measured slower at these sizes -- 4.7 against 2.7 ms for four layers of 2,048 tokens --
+    // because it leaves a quarter of the threads and the token-by-token chain is what is waited for)
     if (N <= 64) return launch_scan<4, 16, ROW>(p, n_seqs, max_new, 8, stream);
     if (N <= 128) return launch_scan<8, 16, ROW>(p, n_seqs, max_new, 8, stream);
     if (N <= 192) return launch_scan<12, 16, ROW>(p, n_seqs, max_new, 8, stream);
