@@ -1,12 +1,17 @@
-// Attention over the paged key/value cache, general form: any head size that is a multiple of 16 up
-// to 256, any number of heads and groups, float32 or bfloat16, prompts and single tokens alike.
+// Attention over the paged key/value cache, general form: any head size up to 256, any number of heads
+// and groups, float32 or bfloat16, prompts and single tokens alike.
 //
-//   qkv_post   per token and head: optional weightless RMS norm of q and k, rotary position encoding,
-//              optional query temperature; writes q to its buffer and k, v into the cache pages.
-//   attention  one block per (token, head): scores over the keys the window allows, softmax and the
-//              weighted sum of values in float32, keys visited in position order.  A position encoding
-//              that acts on the scores hands in a table: score(query at p, key at t) += bias[head][min(p - t,
-//              n_dist - 1)].
+//   qkv_post     per token and head: optional weightless RMS norm of q and k, rotary position encoding,
+//                optional query temperature; writes q to its buffer and k, v into the cache pages
+//                (head sizes that are multiples of 16).
+//   qkv_prepare  the same step for mixers with biases, an RMS norm over the whole q and the whole k projection
+//                (with weights), a rotation of only the first elements of each head, or values of another size
+//                than keys; a block per token, float32 or bfloat16 rows in.
+//   attention    one block per (token, head): scores over the keys the window allows, softmax and the
+//                weighted sum of values in float32, keys visited in position order.  A position encoding
+//                that acts on the scores hands in a table: score(query at p, key at t) += bias[head][min(p - t,
+//                n_dist - 1)].  A sink (a number per head) joins the softmax denominator as exp(sink), with no
+//                key and no value.  Values may have another size than keys.
 //
 // Formulas (file:line of kurulav1/cpi): per-head norm src/engine/llama4_cpu_engine.cpp:308-317; RoPE pairs
 // (d, d + D/2) with angle float(p) * theta_d :167-193, :467; scores, softmax with 1/max(sum, 1e-20) and
