@@ -740,7 +740,8 @@ def run_veredra(args) -> dict:
                 "prefill": frac(vp.get("scan", 0) / reps, nbytes=sum(scan_prefill_bytes.values())),
                 "decode": frac(vd.get("scan", 0) / reps, nbytes=sum(scan_decode_bytes.values()))}},
             "norms_and_residual": {
-                "veredra": {"prefill": frac(vp.get("rmsnorm", 0) / n_layers, nbytes=T * W * (3 * 2 * 2 * 4 + 2 * 4 + 2 * 2.0))},
+                # two stream kernels a layer: each reads and writes both float32 streams, reads y, writes h
+                "veredra": {"prefill": frac(vp.get("rmsnorm", 0) / n_layers, nbytes=T * W * 2 * (2 * 2 * 4 + 4 + 2.0))},
                 "dense": {"prefill": frac(lp.get("rmsnorm", 0) / n_layers, nbytes=T * W * 2 * (4 + 2.0))}},
         }
         out["points"][name] = {"sizes": sz, "layers": n_layers, "prefill_tokens": T, "decode_batch": B,

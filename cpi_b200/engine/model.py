@@ -127,6 +127,7 @@ class DecoderModel:
         T, H, S = batch.n_tokens, self.spec.hidden_size, self.streams
         # the residual: float32 [T, H], or [S, T, H] for blocks that keep S streams (each starts as the embedding)
         xs = self.ws.get("residual", (S, T, H), torch.float32)
+        self.ws.pending_writeback = None
         with phase("embedding"):
             for s in range(S):
                 K.embedding(batch.tokens, self.embedding, xs[s], self.err_flag)
@@ -137,7 +138,9 @@ class DecoderModel:
             view = parts_base.CacheView(cache_manager, owner, owns=e.cache_of is None)
             layer.block.run(layer, x, batch, view)
             if self.layer_capture is not None:
+                self.ws.settle()
                 self.layer_capture.append(xs.sum(0))
+        self.ws.settle()                    # a write-back that the last block left to its successor
         R = batch.n_want
         logits = self.ws.get("logits", (R, self.spec.vocab_size), torch.float32)   # valid until the next step
         if R:

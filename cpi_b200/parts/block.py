@@ -7,7 +7,10 @@ at the start; the final norm reads their sum).  Sublayer q (1: mixer, 2: feed-fo
 streams and writes to all of them:
     u = sum_s read_q[s] x_s;   y = sublayer_q(norm_q(u));   x_t <- sum_s mix_q[s, t] x_s + write_q[t] y
 (every x_t from the old streams; mix indexed [from, to]).  One kernel per boundary applies the write-back of the
-sublayer before and forms and normalises the next u.  A layer without a feed-forward has the first sublayer only.
+sublayer before and forms and normalises the next u; the write-back of a layer's last sublayer is left pending in
+the workspace and done by the next layer's first kernel (or by `Workspace.settle()` when something else reads the
+residual first), so a layer costs as many of these launches as it has sublayers.  A layer without a feed-forward
+has the first sublayer only.
 """
 from __future__ import annotations
 
@@ -26,6 +29,7 @@ class PreNormBlock(Block):
         super().__init__(spec, prefix)
 
     def run(self, layer, residual, batch, cache):
+        layer.mixer_norm.ws.settle()        # a block of another kind may have left its last write-back pending
         with phase("rmsnorm"):
             h = layer.mixer_norm(residual, batch.dtype)
         layer.mixer.forward(h, residual, batch, cache)
@@ -95,8 +99,14 @@ class HyperConnectionsBlock(Block):
         x = residual if residual.dim() == 3 else residual.unsqueeze(0)
         T, H = x.shape[1], x.shape[2]
         ws = layer.mixer_norm.ws
+        before, ws.pending_writeback = ws.pending_writeback, None
+        if before is not None and before[0].data_ptr() != x.data_ptr():
+            ws.pending_writeback = before          # another residual's: not ours to fuse
+            ws.settle()
+            before = None
         with phase("rmsnorm"):
-            h = self._sublayer(x, layer.mixer_norm, self.coef[0], None, batch.dtype, "norm_mixer")
+            h = self._sublayer(x, layer.mixer_norm, self.coef[0], None if before is None else (before[1], (None, before[2], before[3])),
+                               batch.dtype, "norm_mixer")
         y = ws.get("hc_y", (T, H), torch.float32)
         self._run_part(layer.mixer, h, y, batch, cache)
         pending = (y, self.coef[0])
@@ -106,5 +116,4 @@ class HyperConnectionsBlock(Block):
             y2 = ws.get("hc_y2", (T, H), torch.float32)
             self._run_part(layer.feed_forward, h2, y2, batch)
             pending = (y2, self.coef[1])
-        with phase("rmsnorm"):
-            K.hc_step(x, y=pending[0], write=pending[1][1], mix=pending[1][2])
+        ws.pending_writeback = (x, pending[0], pending[1][1], pending[1][2])

@@ -9,6 +9,17 @@ class Workspace:
         self.device = device
         self._buffers: dict = {}
         self.generation = 0        # grows whenever a buffer is (re)allocated: captured graphs then hold stale addresses
+        # A block may leave the write-back of its last sublayer to whoever touches the residual next (the next
+        # block fuses it with its first read): (streams x, y, write weights, mixing matrix) or None.  Whoever
+        # reads the residual without knowing about it calls `settle()` first.
+        self.pending_writeback = None
+
+    def settle(self) -> None:
+        """Applies a write-back that a block has left pending (see `pending_writeback`)."""
+        p, self.pending_writeback = self.pending_writeback, None
+        if p is not None:
+            from ..csrc import lib as K
+            K.hc_step(p[0], y=p[1], write=p[2], mix=p[3])
 
     def get(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
         n = 1

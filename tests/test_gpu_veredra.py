@@ -4,6 +4,7 @@ far keys, long decoding, other sizes, generation through the entry point, and th
 from __future__ import annotations
 
 import json
+import math
 import os
 import subprocess
 import sys
@@ -260,6 +261,64 @@ def test_gelu_gate_in_the_product_epilogue(T, I, H, dtype):
     ref = P.gelu_tanh(gu[:, :I]) * gu[:, I:]
     tol = 1e-5 if dtype == torch.float32 else 2e-2
     assert (out.double() - ref).abs().max() < tol * ref.abs().max()
+
+
+def _sink_reference(q, k, v, pos, lo, scale, sink):
+    """q [NH, D] at position `pos` over keys lo..pos of k, v [n, NKV, D]; exp(sink[h]) joins the denominator."""
+    q, k, v, sink = q.cpu(), k.cpu(), v.cpu(), sink.cpu()
+    NH, G = q.shape[0], q.shape[0] // k.shape[1]
+    out = torch.empty(NH, v.shape[-1], dtype=torch.float64)
+    for h in range(NH):
+        sc = (k[lo:pos + 1, h // G].double() @ q[h].double()) * scale
+        top = max(sc.max().item(), sink[h].item())
+        e = torch.exp(sc - top)
+        out[h] = (e / (e.sum() + math.exp(sink[h].item() - top))) @ v[lo:pos + 1, h // G].double()
+    return out
+
+
+@pytest.mark.parametrize("NH,NKV,D,window", [(8, 2, 128, ("sliding", 130)), (6, 6, 64, ("sliding", 64)),
+                                             (4, 1, 64, ("full", 0))])
+def test_sink_in_all_three_attention_kernels(NH, NKV, D, window):
+    """A sink per head, from far below the scores to far above them, in the general kernel, in the tensor-core
+    decode kernel (one split and several) and in the tensor-core prefill kernel."""
+    import test_gpu_kernels as TK
+    page, (wk, wsz), scale = 64, window, 1.0 / math.sqrt(D)
+    sink = (torch.linspace(-6.0, 9.0, NH) + 0.3).cuda()
+    low = lambda pos: 0 if wk == "full" else max(0, pos - wsz + 1)
+    lengths = [1, 64, 65, 500, 129]
+    k, v, table = TK.paged_cache(len(lengths), lengths, NKV, D, page, torch.bfloat16, seed=3)
+    T = len(lengths)
+    q = TK.rnd(T, NH * D, dtype=torch.bfloat16, seed=4)
+    token_seq = torch.arange(T, dtype=torch.int32, device="cuda")
+    token_pos = torch.tensor([l - 1 for l in lengths], dtype=torch.int32, device="cuda")
+    seq_slot = torch.arange(1, T + 1, dtype=torch.int32, device="cuda")
+    kw = dict(n_heads=NH, n_kv_heads=NKV, head_dim=D, window_kind=K().WINDOW_KINDS[wk], window_size=wsz, scale=scale)
+    refs = []
+    for i, l in enumerate(lengths):
+        kk, vv = TK.gather_kv(k, table, i + 1, l, page), TK.gather_kv(v, table, i + 1, l, page)
+        refs.append(_sink_reference(q[i].float().view(NH, D), kk, vv, l - 1, low(l - 1), scale, sink).reshape(-1))
+    outs = {}
+    outs["general"] = torch.empty_like(q)
+    K().attention_general(q, outs["general"], k, v, table, page, token_seq, token_pos, seq_slot, sink=sink, **kw)
+    for splits in (1, 5):
+        outs[f"decode{splits}"] = torch.empty_like(q)
+        K().attention_decode(q, outs[f"decode{splits}"], k, v, table, page, token_seq, token_pos, seq_slot,
+                             n_splits=splits, sink=sink, **kw)
+    for name, out in outs.items():
+        for i in range(T):
+            e = (out[i].double().cpu() - refs[i]).abs().max().item()
+            assert e <= 1.5e-2 * max(1.0, refs[i].abs().max().item()), (name, i, e)
+    c = TK._prefill_case(NH, NKV, D, window, [(0, 1), (0, 300), (70, 200), (100, 140)], tile=256)
+    out = torch.full_like(c["q"], float("nan"))
+    K().attention_prefill(c["q"], out, c["k"], c["v"], c["table"], page, c["token_seq"], c["token_pos"], c["seq_slot"],
+                          c["tile_tok0"], c["tile_rows"], sink=sink, **kw)
+    torch.cuda.synchronize()
+    kk = [TK.gather_kv(torch.nan_to_num(c["k"]), c["table"], i + 1, l, page) for i, l in enumerate(c["lengths"])]
+    vv = [TK.gather_kv(torch.nan_to_num(c["v"]), c["table"], i + 1, l, page) for i, l in enumerate(c["lengths"])]
+    for t, (sq, pos) in enumerate(zip(c["seq"], c["pos"])):
+        ref = _sink_reference(c["q"][t].float().view(NH, D), kk[sq], vv[sq], pos, low(pos), scale, sink).reshape(-1)
+        e = (out[t].double().cpu() - ref).abs().max().item()
+        assert e <= 1.5e-2 * max(1.0, ref.abs().max().item()), ("prefill", t, sq, pos, e)
 
 
 # ---- each mixer alone, as a one-layer model --------------------------------------------------------------
