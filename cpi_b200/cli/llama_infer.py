@@ -279,8 +279,11 @@ def _main(argv=None) -> int:
                 ms = timer.collect().get("decode", {})
             finally:
                 model.engine.profile_phases(False)
+            # the reference's phases in its order, then whatever else the model's parts bracket (a recurrent
+            # mixer's convolution and scan, say)
+            more = tuple(sorted(n for n in ms if n not in PHASES and n != "embedding"))
             print(f"[bench-phase{'-avg' if repeated else ''}]"
-                  + "".join(f" {name}_ms={ms.get(name, 0.0) / reps:.2f}" for name in PHASES))
+                  + "".join(f" {name}_ms={ms.get(name, 0.0) / reps:.2f}" for name in PHASES + more))
         return 0
     except Exception as e:                                    # noqa: BLE001  (the reference: catch, print, 2)
         print(f"fatal: {type(e).__name__}: {e}", file=sys.stderr)

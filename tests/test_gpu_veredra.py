@@ -544,6 +544,27 @@ def test_greedy_generation_through_the_entry_point(models):
         assert len(res.tokens) == 12
 
 
+def test_command_line_generates_with_a_veredra_folder(models):
+    """bin/llama_infer knows the family by its config.json: greedy tokens are the plain implementation's, and the
+    phase report names the recurrent mixers' phases."""
+    b = models["C"]
+    prompt = V.tokens(9, b.cfg["vocab"], 50)
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "llama_infer"), b.dir, "--tokens",
+                        ",".join(map(str, prompt)), "--max-new", "6", "--temp", "0", "--dtype", "float32",
+                        "--benchmark-phases", "--max-context", "64"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    line = next(l for l in r.stdout.splitlines() if l.startswith("Output tokens:"))
+    got = [int(x) for x in line.split(":")[1].split()]
+    assert got[:9] == prompt and len(got) == 15
+    seq = list(prompt)
+    for tok in got[9:]:
+        ref = b.plain(seq)[-1]
+        best = int(ref.argmax())
+        assert tok == best or (ref[best] - ref[tok]).item() < 1e-3 * ref.abs().max().item()
+        seq.append(tok)
+    assert "Veredra" in r.stdout and "scan" in r.stdout
+
+
 def test_replay_tool_runs_a_veredra_folder(models, tmp_path):
     """bin/trace_run in a process of its own: a request whole, and two requests batched then decoded."""
     b = models["B"]
