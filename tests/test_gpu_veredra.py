@@ -111,7 +111,7 @@ class FakeBatch:
 
     def __init__(self, slots, starts, n_new, dev):
         i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
-        self.n_seqs = len(slots)
+        self.n_seqs, self.max_new = len(slots), max(n_new)
         self.seq_slot, self.seq_start, self.seq_new = i32(slots), i32(starts), i32(n_new)
         tok0, seq, pos, base = [], [], [], 0
         for s, (st, n) in enumerate(zip(starts, n_new)):
@@ -119,11 +119,12 @@ class FakeBatch:
         self.seq_tok0, self.token_seq, self.token_pos = i32(tok0), i32(seq), i32(pos)
 
 
-@pytest.mark.parametrize("S", [1, 2, 3, 5])
-def test_stream_mixing_kernel(S):
+@pytest.mark.parametrize("S,Wd", [(1, 100), (2, 100), (3, 2048), (5, 100), (8, 5000)])
+def test_stream_mixing_kernel(S, Wd):
     """Write-back of one sublayer and read of the next: x_t <- sum_s M[s, t] x_s + b[t] y, u = sum_s a[s] x_s,
-    h = u * rsqrt(mean u^2 + eps) * (1 + w); then the read alone over chosen rows."""
-    dev, T, Wd = "cuda", 7, 100
+    h = u * rsqrt(mean u^2 + eps) * (1 + w); then the read alone over chosen rows.  Narrow rows, rows that fill the
+    largest block once, and rows wider than a block's registers hold."""
+    dev, T = "cuda", 7
     g = torch.Generator().manual_seed(S)
     x = torch.randn(S, T, Wd, generator=g).to(dev)
     y, mix, write, read = (torch.randn(*s, generator=g).to(dev) for s in ((T, Wd), (S, S), (S,), (S,)))
@@ -169,11 +170,13 @@ def test_causal_convolution_with_carried_inputs(taps):
         done = [d + c for d, c in zip(done, cut)]
 
 
-@pytest.mark.parametrize("rows,cols,heads,per_group", [(24, 20, 6, 2), (64, 33, 2, 1), (130, 16, 3, 3), (8, 5, 4, 4)])
+@pytest.mark.parametrize("rows,cols,heads,per_group", [(24, 20, 6, 2), (64, 33, 2, 1), (130, 16, 3, 3), (8, 5, 4, 4),
+                                                       (96, 12, 2, 2), (200, 9, 1, 1), (300, 8, 2, 1), (600, 4, 1, 1)])
 def test_recurrence_kernel_both_flavours(rows, cols, heads, per_group):
-    """S_t = diag(a_t) S_{t-1} + k_t v_t^T, o_t = S_t^T q_t over a sequence cut as 6 + 1 + 1 + 4 beside a second one,
-    with a decay per row (sigmoid(z + b)^(1/tau)) and with a decay per head (softplus step, skip term)."""
-    dev, n = "cuda", 12
+    """S_t = diag(a_t) S_{t-1} + k_t v_t^T, o_t = S_t^T q_t over a sequence cut as 20 + 1 + 1 + 6 + 18 beside a second
+    one, with a decay per row (sigmoid(z + b)^(1/tau)) and with a decay per head (softplus step, skip term).  Long
+    portions take the kernel's wide blocks and short ones its narrow blocks, on the same state."""
+    dev, n = "cuda", 46
     g = torch.Generator().manual_seed(rows)
     groups = heads // per_group
     k, q = torch.randn(n, groups * rows, generator=g), torch.randn(n, groups * rows, generator=g)
@@ -206,7 +209,7 @@ def test_recurrence_kernel_both_flavours(rows, cols, heads, per_group):
         state = torch.full((3, heads, rows, cols), 3.0, device=dev)
         state[2].zero_(); state[0].zero_()
         done = 0
-        for cut in (6, 1, 1, 4):
+        for cut in (20, 1, 1, 6, 18):
             fb = FakeBatch([2, 0], [done, done], [cut, cut], dev)          # the same sequence twice, in two slots
             sl = slice(done, done + cut)
             two = lambda t: torch.cat([t[sl], t[sl]]).to(dev).contiguous()
