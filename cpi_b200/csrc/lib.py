@@ -409,11 +409,12 @@ def causal_conv(x, weight, bias, carry, out, batch, *, silu=True):
 
 
 def linear_scan(k, q, v, state, out, batch, *, n_heads, heads_per_group, n_rows, n_cols, z=None, z_bias=None,
-                tau=1.0, dt=None, dt_bias=None, a_log=None, skip=None, q_scale=1.0):
+                tau=1.0, dt=None, dt_bias=None, a_log=None, skip=None, q_scale=1.0, decay_ready=False):
     """The recurrence S_t = diag(a_t) S_{t-1} + k_t v_t^T, o_t = S_t^T q_t (+ skip v_t) per sequence and head over the
     state [slots, heads, n_rows, n_cols] (float32, updated in place).  Give `z` [T, heads * n_rows] for a decay per
     row, a = sigmoid(z + z_bias)^(1 / tau); or `dt` [T, heads] for a decay per head with a step size,
-    dt' = softplus(dt + dt_bias), a = exp(-exp(a_log) dt'), v' = dt' v.  All rows float32 (column slices allowed)."""
+    dt' = softplus(dt + dt_bias), a = exp(-exp(a_log) dt'), v' = dt' v.  All rows float32 (column slices allowed).
+    `decay_ready`: `z` already holds a (`row_decay` ran over it).  `q_scale` multiplies the outputs' S^T q."""
     small = [t for t in (z_bias, dt_bias, a_log, skip) if t is not None]
     _need_cuda(k, q, v, state, out, z, dt, *small)
     for t in (k, q, v, out, z, dt):
@@ -426,8 +427,20 @@ def linear_scan(k, q, v, state, out, batch, *, n_heads, heads_per_group, n_rows,
           _p(dt), c_long(0 if dt is None else dt.stride(0)), _p(dt_bias), _p(a_log), _p(skip), c_int(dtype_code(sd)),
           c_float(q_scale), _p(state), _p(out), c_long(out.stride(0)), _p(batch.seq_slot), _p(batch.seq_tok0),
           _p(batch.seq_new), c_int(batch.n_seqs), c_int(getattr(batch, "max_new", 1 << 20)), c_int(n_heads),
-          c_int(heads_per_group), c_int(n_rows), c_int(n_cols),
+          c_int(heads_per_group), c_int(n_rows), c_int(n_cols), c_int(int(decay_ready)),
           _stream())
+
+
+def row_decay(z, z_bias, tau):
+    """z <- sigmoid(z + z_bias)^(1 / tau) in place, z [T, n] float32 rows: the decays of `linear_scan`'s row flavour,
+    prepared once per element for a step of many tokens (the recurrence computes the same expression itself when
+    it is not given them)."""
+    _need_cuda(z, z_bias)
+    assert z.dtype == torch.float32 and z.dim() == 2 and z.stride(1) == 1
+    assert z_bias is None or (z_bias.is_contiguous() and z_bias.numel() == z.shape[1])
+    _call("cpi_row_decay", _p(z), c_long(z.stride(0)), _p(z_bias),
+          c_int(F32 if z_bias is None else dtype_code(z_bias.dtype)), c_float(1.0 / float(tau)), c_int(z.shape[0]),
+          c_int(z.shape[1]), _stream())
 
 
 def gated_norm(y, gate, weight, out, *, parts, gate_first, eps):

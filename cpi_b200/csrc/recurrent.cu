@@ -93,10 +93,27 @@ struct ScanParams {
   int n_heads, heads_per_group, n_rows, n_cols;      // H, H / groups, N, Dv
   int chunk;                             // tokens staged in shared memory at a time
   int vec16;                             // the rows of k, q and z start on 16-byte boundaries and N is a multiple of 4
+  int decay_ready;                       // z already holds the decays a (row_decay ran over it)
 };
 
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
 __device__ __forceinline__ float log_sigmoid_f(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
+// a = sigmoid(z + b)^(1 / tau); one function for the kernel that prepares a prompt's decays and for the recurrence
+// that computes a decoded token's own, so that both give the same bits
+__device__ __forceinline__ float row_decay_f(float z, float b, float inv_tau) { return expf(log_sigmoid_f(z + b) * inv_tau); }
+
+struct RowDecayParams { float* z; long z_stride; const void* bias; int bias_dtype; float inv_tau; int n; };
+
+// z[t, i] <- sigmoid(z[t, i] + bias[i])^(1 / tau), in place: the decays of a step of many tokens, once per element
+// instead of once per block of columns inside the recurrence
+__global__ void __launch_bounds__(256) row_decay_kernel(RowDecayParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int i = blockIdx.y * blockDim.x + threadIdx.x;
+  if (i >= p.n) return;
+  float* z = p.z + (size_t)blockIdx.x * p.z_stride + i;
+  *z = row_decay_f(*z, p.bias ? load_any(p.bias, p.bias_dtype, i) : 0.f, p.inv_tau);
+}
 
 __device__ __forceinline__ void cp_async4(float* dst_smem, const float* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst_smem))), "l"(src) : "memory");
@@ -112,8 +129,8 @@ template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile(
 // through shared memory a chunk at a time, in two buffers: while one chunk is computed the next one's rows (k, q,
 // the decays before their transform, the block's columns of v, the raw step sizes) are on their way as
 // asynchronous copies, 16 bytes each where the rows allow it.  Once a chunk has landed, one pass turns what was
-// copied into what the recurrence needs (q scaled; a = sigmoid(z + b)^(1/tau), or the step size and the head's
-// decay).  Per token the rows' k, q and a lie as each lane group's NPT values followed by four words of padding,
+// copied into what the recurrence needs (a = sigmoid(z + b)^(1/tau) unless the caller prepared it, or the step
+// size and the head's decay); q's constant scale multiplies the output sum.  Per token the rows' k, q and a lie as each lane group's NPT values followed by four words of padding,
 // so that the 16-byte reads of different kk fall into different banks.
 template <int NPT, int KS, bool ROW_DECAY, int CPT>
 __global__ void __launch_bounds__(256) linear_scan_kernel(ScanParams p) {
@@ -208,13 +225,13 @@ __global__ void __launch_bounds__(256) linear_scan_kernel(ScanParams p) {
     __syncthreads();
     // what was copied becomes what the recurrence needs
     float *ks = k_of(b), *qs = q_of(b), *ds = d_of(b), *vs = v_of(b), *dts = dt_of(b), *as = a_of(b);
-    if (ROW_DECAY || p.q_scale != 1.0f) {
+    const bool transform = ROW_DECAY ? !p.decay_ready : true;
+    if (ROW_DECAY && transform) {
       for (int e = tid; e < nc * KS * NPT; e += blockDim.x) {
         const int j = e / (KS * NPT), n = e % (KS * NPT);
         if (n >= N) continue;
         const int at = j * ROWP + (n / NPT) * (NPT + 4) + n % NPT;
-        qs[at] *= p.q_scale;
-        if (ROW_DECAY) ds[at] = expf(log_sigmoid_f(ds[at] + bias_s[n]) * p.inv_tau);
+        ds[at] = row_decay_f(ds[at], bias_s[n], p.inv_tau);
       }
     }
     if (!ROW_DECAY) {
@@ -224,7 +241,7 @@ __global__ void __launch_bounds__(256) linear_scan_kernel(ScanParams p) {
         as[j] = expf(head_a * dt);
       }
     }
-    __syncthreads();
+    if (transform) __syncthreads();
 #pragma unroll 1
     for (int j = 0; j < nc; ++j) {
       const float4* k4 = reinterpret_cast<const float4*>(ks + j * ROWP + kk * (NPT + 4));
@@ -256,7 +273,7 @@ __global__ void __launch_bounds__(256) linear_scan_kernel(ScanParams p) {
 #pragma unroll
         for (int off = PVW; off < 32; off <<= 1) o[c] += __shfl_xor_sync(0xffffffffu, o[c], off);
         if (kk == 0 && col + c < Dv)
-          p.out[(size_t)(tok0 + c0 + j) * p.out_stride + (size_t)h * Dv + col + c] = fmaf(head_skip, v_raw[c], o[c]);
+          p.out[(size_t)(tok0 + c0 + j) * p.out_stride + (size_t)h * Dv + col + c] = fmaf(head_skip, v_raw[c], o[c] * p.q_scale);
       }
     }
     __syncthreads();                                         // the buffer may be copied into again
@@ -405,7 +422,7 @@ extern "C" int cpi_linear_scan(const float* k, long k_stride, const float* q, lo
                                const void* skip, int small_dtype, float q_scale, float* state, float* out,
                                long out_stride, const int* seq_slot, const int* seq_tok0, const int* seq_new,
                                int n_seqs, int max_new, int n_heads, int heads_per_group, int n_rows, int n_cols,
-                               cudaStream_t stream) {
+                               int decay_ready, cudaStream_t stream) {
   if (n_seqs == 0) return 0;
   CPI_REQUIRE((z != nullptr) != (dt != nullptr), "linear_scan: give row decays or step sizes, one of the two");
   CPI_REQUIRE(dt == nullptr || a_log != nullptr, "linear_scan: step sizes need the heads' decay rates");
@@ -414,9 +431,18 @@ extern "C" int cpi_linear_scan(const float* k, long k_stride, const float* q, lo
   CPI_REQUIRE(n_heads <= 65535, "linear_scan: too many heads (%d)", n_heads);
   ScanParams p{k, k_stride, q, q_stride, v, v_stride, z, z_stride, z_bias, inv_tau, dt, dt_stride, dt_bias, a_log,
                skip, small_dtype, q_scale, state, out, out_stride, seq_slot, seq_tok0, seq_new,
-               n_heads, heads_per_group, n_rows, n_cols, 0};
+               n_heads, heads_per_group, n_rows, n_cols, 0, 0, decay_ready};
   if (max_new < 1) max_new = 1;
   return z ? dispatch_scan<true>(p, n_seqs, max_new, stream) : dispatch_scan<false>(p, n_seqs, max_new, stream);
+}
+
+extern "C" int cpi_row_decay(float* z, long z_stride, const void* bias, int bias_dtype, float inv_tau, int n_tokens,
+                             int n, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  CPI_REQUIRE(n > 0, "row_decay: %d elements a row", n);
+  RowDecayParams p{z, z_stride, bias, bias_dtype, inv_tau, n};
+  cpi::launch_pdl(row_decay_kernel, dim3(n_tokens, (n + 255) / 256), 256, 0, stream, p);
+  return check_launch("row_decay");
 }
 
 extern "C" int cpi_gated_norm(const float* y, long y_stride, const float* gate, long gate_stride, const void* w,

@@ -32,6 +32,9 @@ from ..weights.store import TensorReq
 from .base import Mixer, register_mixer
 from .linear import MODE_ADD, MODE_STORE, project
 
+# steps whose longest portion has more tokens than this prepare the row decays with a kernel of their own
+DECAY_PREPASS_FROM = 16
+
 
 def _cat_rows(tensors):
     dt = torch.float32 if any(t.dtype == torch.float32 for t in tensors) else torch.bfloat16
@@ -163,9 +166,15 @@ class GLAMixer(Mixer):
             project(low, self.w_a2, z)
         o = self.ws.get("gla_o", (T, nv), f32)
         with phase("scan"):
+            # a step of many tokens prepares its decays once per element; a decode step leaves them to the
+            # recurrence (one launch less), which computes the same expression
+            ready = batch.max_new > DECAY_PREPASS_FROM
+            if ready:
+                K.row_decay(z, self.b_a2, self.tau)
             K.linear_scan(proj[:, nk:2 * nk], proj[:, :nk], proj[:, 2 * nk:2 * nk + nv], cache.state("s"), o, batch,
-                          n_heads=self.nh, heads_per_group=1, n_rows=self.dk, n_cols=self.dv, z=z, z_bias=self.b_a2,
-                          tau=self.tau, q_scale=self.dk ** -0.5)
+                          n_heads=self.nh, heads_per_group=1, n_rows=self.dk, n_cols=self.dv, z=z,
+                          z_bias=None if ready else self.b_a2, tau=self.tau, q_scale=self.dk ** -0.5,
+                          decay_ready=ready)
         with phase("gated_norm"):
             g = self.ws.get("gla_gated", (T, nv), h.dtype)
             K.gated_norm(o, proj[:, 2 * nk + nv:], self.w_norm, g, parts=self.nh, gate_first=False, eps=self.eps)

@@ -216,7 +216,15 @@ def test_recurrence_kernel_both_flavours(rows, cols, heads, per_group):
             out = torch.empty(2 * cut, heads * cols, device=dev)
             kw = dict(n_heads=heads, heads_per_group=per_group, n_rows=rows, n_cols=cols)
             if row_decay:
+                before = state.clone()
                 K().linear_scan(two(k), two(q), two(v), state, out, fb, z=two(z), z_bias=zb.to(dev), tau=4.0, q_scale=0.5, **kw)
+                # decays prepared by their own kernel: the same bits in the outputs and in the state
+                a, out2 = two(z), torch.empty_like(out)
+                K().row_decay(a, zb.to(dev), 4.0)
+                want_a = torch.exp(torch.nn.functional.logsigmoid(two(z).double() + zb.to(dev).double()) / 4.0)
+                assert (a.double() - want_a).abs().max() < 1e-6
+                K().linear_scan(two(k), two(q), two(v), before, out2, fb, z=a, tau=4.0, q_scale=0.5, decay_ready=True, **kw)
+                assert torch.equal(out, out2) and torch.equal(state, before)
             else:
                 K().linear_scan(two(k), two(q), two(v), state, out, fb, dt=two(dt), dt_bias=dtb.to(dev),
                                 a_log=a_log.to(dev), skip=skip.to(dev), **kw)
