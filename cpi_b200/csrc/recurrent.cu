@@ -168,12 +168,17 @@ __global__ void __launch_bounds__(256) linear_scan_kernel(ScanParams p) {
   pdl_wait();
   const int n_tok = p.seq_new[s], tok0 = p.seq_tok0[s];
   float* st = p.state + (((size_t)p.seq_slot[s] * H + h) * N) * Dv + col;
-  float S[NPT][CPT];                                         // rows kk * NPT .., columns col .. col + CPT - 1
+  // rows kk * NPT .., columns col .. col + CPT - 1; two neighbouring rows of a column make one pair, so that the
+  // recurrence runs on the packed float32 instructions (each half rounds as the single instruction does)
+  float2 S[NPT / 2][CPT];
 #pragma unroll
   for (int i = 0; i < NPT; ++i) {
     const int n = kk * NPT + i;
 #pragma unroll
-    for (int c = 0; c < CPT; ++c) S[i][c] = (col + c < Dv && n < N) ? st[(size_t)n * Dv + c] : 0.f;
+    for (int c = 0; c < CPT; ++c) {
+      const float s0 = (col + c < Dv && n < N) ? st[(size_t)n * Dv + c] : 0.f;
+      if (i & 1) S[i / 2][c].y = s0; else S[i / 2][c].x = s0;
+    }
   }
   __syncthreads();                                           // the zeros are in place before the first copies land
 
@@ -242,34 +247,42 @@ __global__ void __launch_bounds__(256) linear_scan_kernel(ScanParams p) {
       }
     }
     if (transform) __syncthreads();
-#pragma unroll 1
+#pragma unroll 2
     for (int j = 0; j < nc; ++j) {
       const float4* k4 = reinterpret_cast<const float4*>(ks + j * ROWP + kk * (NPT + 4));
       const float4* q4 = reinterpret_cast<const float4*>(qs + j * ROWP + kk * (NPT + 4));
       const float4* d4 = reinterpret_cast<const float4*>(ds + j * ROWP + kk * (NPT + 4));
-      float v_raw[CPT], vv[CPT], o[CPT];
+      float v_raw[CPT], o[CPT];
+      float2 vv[CPT], o2[CPT];
       float a = 0.f, dtj = 1.f;
       if (!ROW_DECAY) { dtj = dts[j]; a = as[j]; }
 #pragma unroll
-      for (int c = 0; c < CPT; ++c) { v_raw[c] = vs[j * pvb + lcol + c]; vv[c] = v_raw[c] * dtj; o[c] = 0.f; }
+      for (int c = 0; c < CPT; ++c) {
+        v_raw[c] = vs[j * pvb + lcol + c];
+        vv[c] = make_float2(v_raw[c] * dtj, v_raw[c] * dtj);
+        o2[c] = make_float2(0.f, 0.f);
+      }
       // a thread's rows times its columns: k, q and the decay of a row are read once for all its columns
 #pragma unroll
       for (int i4 = 0; i4 < NPT / 4; ++i4) {
         const float4 kq = k4[i4], qq = q4[i4];
         float4 dd = make_float4(a, a, a, a);
         if (ROW_DECAY) dd = d4[i4];
-        const float kr[4] = {kq.x, kq.y, kq.z, kq.w}, qr[4] = {qq.x, qq.y, qq.z, qq.w}, dr[4] = {dd.x, dd.y, dd.z, dd.w};
+        const float2 kr[2] = {make_float2(kq.x, kq.y), make_float2(kq.z, kq.w)};
+        const float2 qr[2] = {make_float2(qq.x, qq.y), make_float2(qq.z, qq.w)};
+        const float2 dr[2] = {make_float2(dd.x, dd.y), make_float2(dd.z, dd.w)};
 #pragma unroll
-        for (int r = 0; r < 4; ++r) {
+        for (int r = 0; r < 2; ++r) {
 #pragma unroll
           for (int c = 0; c < CPT; ++c) {
-            S[4 * i4 + r][c] = fmaf(kr[r], vv[c], dr[r] * S[4 * i4 + r][c]);
-            o[c] = fmaf(S[4 * i4 + r][c], qr[r], o[c]);
+            S[2 * i4 + r][c] = __ffma2_rn(kr[r], vv[c], __fmul2_rn(dr[r], S[2 * i4 + r][c]));
+            o2[c] = __ffma2_rn(S[2 * i4 + r][c], qr[r], o2[c]);
           }
         }
       }
 #pragma unroll
       for (int c = 0; c < CPT; ++c) {
+        o[c] = o2[c].x + o2[c].y;
 #pragma unroll
         for (int off = PVW; off < 32; off <<= 1) o[c] += __shfl_xor_sync(0xffffffffu, o[c], off);
         if (kk == 0 && col + c < Dv)
@@ -284,7 +297,7 @@ __global__ void __launch_bounds__(256) linear_scan_kernel(ScanParams p) {
     const int n = kk * NPT + i;
 #pragma unroll
     for (int c = 0; c < CPT; ++c)
-      if (col + c < Dv && n < N) st[(size_t)n * Dv + c] = S[i][c];
+      if (col + c < Dv && n < N) st[(size_t)n * Dv + c] = (i & 1) ? S[i / 2][c].y : S[i / 2][c].x;
   }
 }
 
