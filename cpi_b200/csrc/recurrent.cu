@@ -385,7 +385,8 @@ static int dispatch_scan(const ScanParams& p, int n_seqs, int max_new, cudaStrea
     // (sixteen lanes a column: thirty-two were measured slower, 5.0 against 2.7 ms for four layers of 2,048 tokens;
     // what a warp does per token besides its rows' arithmetic -- addresses, the value, the shuffle sum, the
     // store -- then weighs more than the rows.  Taking the shuffle sums of four tokens side by side changed
-    // nothing: 2.6 ms.)
+    // nothing: 2.6 ms.  Measured again with prepared decays and paired rows: 4.4 against 2.2 ms; twice the blocks
+    // stage and read twice the rows of k, q and the decays.)
     if (N <= 64) return launch_scan<4, 16, ROW>(p, n_seqs, max_new, 8, stream);
     if (N <= 128) return launch_scan<8, 16, ROW>(p, n_seqs, max_new, 8, stream);
     if (N <= 192) return launch_scan<12, 16, ROW>(p, n_seqs, max_new, 8, stream);
