@@ -15,7 +15,8 @@ src/engine/llama4_cuda_engine.cu:258-265).  Here:
   group, for every stream alike.  Positions at or beyond a sequence's length are never read.
 * A group with a window gives back, at the start of a step, the blocks that no later position can
   see (all positions before the chunk that holds the sequence's next position, or before the last
-  `size` positions).
+  `size` positions).  A sliding window may keep a sequence's first `keep_first` positions visible for
+  good: the blocks that hold them are never given back while the sequence lives.
 * **State**: a mixer may declare named tensors of fixed shape per sequence; they are kept as
   `[slots, *shape]` per run entry and zeroed when a slot is acquired.
 
@@ -46,6 +47,7 @@ class KVRequirement:
     window_kind: str = "full"       # "full" | "chunk" | "sliding"
     window_size: int = 0
     streams: tuple = ()             # () = (("k", n_kv_heads, head_dim), ("v", n_kv_heads, head_dim))
+    keep_first: int = 0             # sliding window: the sequence's first positions stay readable whatever the distance
 
     def stream_shapes(self) -> tuple:
         return self.streams or (("k", self.n_kv_heads, self.head_dim), ("v", self.n_kv_heads, self.head_dim))
@@ -57,6 +59,12 @@ class KVRequirement:
         if self.window_kind == "sliding":
             return max(0, next_pos - self.window_size + 1)
         return 0
+
+    def droppable(self, block: int, next_pos: int, page_size: int) -> bool:
+        """May the block (positions block * page_size ...) be given back before a step that starts at `next_pos`?"""
+        if block >= self.first_needed_position(next_pos) // page_size:
+            return False
+        return not (self.window_kind == "sliding" and block * page_size < self.keep_first)
 
 
 @dataclass(frozen=True)
@@ -128,8 +136,7 @@ class KVGroup:
     def ensure(self, slot: int, length: int, n_new: int) -> None:
         """Free what the window no longer needs, then hold a page for every block of [length, length+n_new)."""
         held = self.blocks[slot]
-        first = self.req.first_needed_position(length) // self.page_size
-        for b in [b for b in held if b < first]:
+        for b in [b for b in held if self.req.droppable(b, length, self.page_size)]:
             self.pool.give_back(held.pop(b))
         if n_new <= 0:
             return
@@ -209,6 +216,8 @@ class CacheManager:
             return self.n_pages
         span = min(self.max_seq_len, req.window_size - 1 + min(self.max_step_tokens, self.max_seq_len))
         per_seq = -(-span // self.page_size) + 1          # a span that starts inside a page touches one page more
+        if req.window_kind == "sliding" and req.keep_first > 0:
+            per_seq += -(-min(req.keep_first, self.max_seq_len) // self.page_size)      # the kept first positions
         return max(1, min(self.n_pages, self.max_slots * per_seq))
 
     # ---- slots ---------------------------------------------------------------------------------
@@ -267,8 +276,7 @@ class CacheManager:
                 for s, n in zip(slots, n_new):
                     h = held.setdefault(s, set(g.blocks[s]))
                     length = at.get(s, self.lengths[s])
-                    first = g.req.first_needed_position(length) // ps
-                    gone = {b for b in h if b < first}
+                    gone = {b for b in h if g.req.droppable(b, length, ps)}
                     free += len(gone)
                     h -= gone
                     for b in range(length // ps, (length + n - 1) // ps + 1):

@@ -54,6 +54,7 @@ class RunEntry:
     """
     layer: int
     cache_of: Optional[int] = None
+    before: Optional[str] = None       # name of a junction (`ModelSpec.junctions`) that rewrites the residual first
 
 
 @dataclass(frozen=True)
@@ -74,6 +75,8 @@ class ModelSpec:
     initializer_range: float = 0.02
     residual_streams: int = 1      # copies of the residual that the layers' blocks keep (hyper-connections); all
                                    # start as the embedding output and the final norm reads their sum
+    junctions: tuple = ()          # of (name, PartSpec): parts that a run entry may name in `before`
+                                   # (`embedding` may carry "norm": a norm PartSpec applied to the looked-up rows)
 
     def validate(self) -> None:
         if not self.run_order:
@@ -81,6 +84,10 @@ class ModelSpec:
         for i, e in enumerate(self.run_order):
             if not 0 <= e.layer < len(self.layers):
                 raise ValueError(f"run_order[{i}] names layer {e.layer} of {len(self.layers)}")
+            if e.before is not None and e.before not in dict(self.junctions):
+                raise ValueError(f"run_order[{i}].before names the junction '{e.before}', which the spec does not have")
+            if e.before is not None and self.residual_streams != 1:
+                raise ValueError("a junction rewrites the one residual; it does not combine with several streams")
             if e.cache_of is not None:
                 if not 0 <= e.cache_of < i:
                     raise ValueError(f"run_order[{i}].cache_of must name an earlier entry, got {e.cache_of}")

@@ -6,7 +6,8 @@
 //                (head sizes that are multiples of 16).
 //   qkv_prepare  the same step for mixers with biases, an RMS norm over the whole q and the whole k projection
 //                (with weights), a rotation of only the first elements of each head, or values of another size
-//                than keys; a block per token, float32 or bfloat16 rows in.
+//                than keys, or a weightless RMS norm of every q and k head after the rotation; a block per token,
+//                float32 or bfloat16 rows in.
 //   attention    one block per (token, head): scores over the keys the window allows, softmax and the
 //                weighted sum of values in float32, keys visited in position order.  A position encoding
 //                that acts on the scores hands in a table: score(query at p, key at t) += bias[head][min(p - t,
@@ -16,7 +17,8 @@
 // Formulas (file:line of kurulav1/cpi): per-head norm src/engine/llama4_cpu_engine.cpp:308-317; RoPE pairs
 // (d, d + D/2) with angle float(p) * theta_d :167-193, :467; scores, softmax with 1/max(sum, 1e-20) and
 // value sum :195-250.  Windows, layers without RoPE, interleaved pairing and the query temperature
-// q *= 1 + a * ln(floor((p + 1) / f) + 1) are this library's own.
+// q *= 1 + a * ln(floor((p + 1) / f) + 1) are this library's own.  A sliding window may keep a sequence's first
+// `keep_first` positions visible to every later query (at their own positions), whatever the distance.
 //
 // Cache layout per layer: [page][kv head][slot in page][D]; a sequence's block b (positions
 // b*PAGE .. b*PAGE+PAGE-1) lives in page page_table[slot * max_blocks + b].
@@ -238,6 +240,7 @@ struct QkvPrepParams {
   const int* page_table; int max_blocks; int page_size;
   const int* token_seq; const int* token_pos; const int* seq_slot;
   int n_heads, n_kv_heads, head_dim, v_dim, write_kv;
+  int head_norm;                         // a weightless RMS norm (norm_eps) of every q and k head, after the rotation
 };
 
 template <typename TI, typename TO>
@@ -275,7 +278,39 @@ __global__ void __launch_bounds__(1024) qkv_prepare_kernel(QkvPrepParams p) {
     kv_row = (size_t)page * p.n_kv_heads * p.page_size + pos % p.page_size;      // row of kv head 0
   }
   const int half = p.rot_dims >> 1;
-  for (int i = tid; i < nq + nk; i += blockDim.x) {
+  float* rot_s = row_s + nq + nk;                        // head_norm: the rotated row, then one factor per head
+  float* inv_s = rot_s + nq + nk;
+  if (p.head_norm) {
+    for (int i = tid; i < nq + nk; i += blockDim.x) {
+      const int e = i < nq ? i : i - nq, d = e % D;
+      float x = row_s[i];
+      if (p.inv_freq && d < p.rot_dims) {
+        const bool first = d < half;
+        const float other = first ? row_s[i + half] : row_s[i - half];
+        float sn, cs;
+        sincosf((float)pos * p.inv_freq[first ? d : d - half], &sn, &cs);
+        x = first ? x * cs - other * sn : x * cs + other * sn;
+      }
+      rot_s[i] = x;
+    }
+    __syncthreads();
+    const int n_heads_all = (nq + nk) / D, warp = tid >> 5, lane = tid & 31;
+    for (int hd = warp; hd < n_heads_all; hd += blockDim.x >> 5) {
+      float ss = 0.f;
+      for (int d = lane; d < D; d += 32) ss = fmaf(rot_s[hd * D + d], rot_s[hd * D + d], ss);
+      ss = warp_sum(ss);
+      if (lane == 0) inv_s[hd] = 1.0f / sqrtf(ss / (float)D + p.norm_eps);
+    }
+    __syncthreads();
+    for (int i = tid; i < nq + nk; i += blockDim.x) {
+      const bool is_q = i < nq;
+      const int e = is_q ? i : i - nq;
+      const float x = rot_s[i] * inv_s[i / D];
+      if (is_q) reinterpret_cast<TO*>(p.q_out)[(size_t)t * nq + i] = from_f32<TO>(x);
+      else reinterpret_cast<TO*>(p.k_cache)[(kv_row + (size_t)(e / D) * p.page_size) * D + e % D] = from_f32<TO>(x);
+    }
+  }
+  for (int i = tid; i < (p.head_norm ? 0 : nq + nk); i += blockDim.x) {
     const bool is_q = i < nq;
     const int e = is_q ? i : i - nq;
     const int hd = e / D, d = e % D;
@@ -319,6 +354,7 @@ struct AttnParams {
   const float* score_bias; int n_dist;   // [NH, n_dist] float32 added to the scaled scores by distance, or null
   const float* sink;                     // [NH] float32 or null: exp(sink[h]) joins the softmax denominator (no key, no value)
   int v_dim;                             // elements of a value row (the cache's v stream); keys have head_dim
+  int keep_first;                        // a sequence's first positions that stay visible below a sliding window
 };
 
 __device__ __forceinline__ int window_low(int kind, int size, int pos) {
@@ -353,9 +389,12 @@ __global__ void __launch_bounds__(ATT_NT) attention_general_kernel(AttnParams p)
   float m_run = -INFINITY, l_run = 0.f, acc0 = 0.f, acc1 = 0.f;
   if (p.sink) { m_run = p.sink[h]; l_run = 1.0f; }
   __syncthreads();
-  for (int base = lo; base <= pos; base += ATT_NT) {
-    const int kp = base + tid;
-    const bool valid = kp <= pos;
+  // the keys a query sees: the kept first positions that lie below the window, then the window
+  const int n_kept = min(p.keep_first, lo), n_keys = n_kept + pos - lo + 1;
+  for (int base = 0; base < n_keys; base += ATT_NT) {
+    const int ki = base + tid;
+    const int kp = ki < n_kept ? ki : lo + ki - n_kept;
+    const bool valid = ki < n_keys;
     float s = -INFINITY;
     if (valid) {
       const int page = table[kp / p.page_size];
@@ -372,7 +411,7 @@ __global__ void __launch_bounds__(ATT_NT) attention_general_kernel(AttnParams p)
     p_s[tid] = e;
     const float l_tile = block_sum(e, scratch);       // its barriers also publish p_s and off_s
     const float alpha = expf(m_run - m_new);
-    const int nv = min(ATT_NT, pos - base + 1);
+    const int nv = min(ATT_NT, n_keys - base);
     acc0 *= alpha; acc1 *= alpha;
     for (int j = 0; j < nv; ++j) {
       const T* vr = vc + off_s[j] * DV;
@@ -439,7 +478,7 @@ extern "C" int cpi_qkv_prepare(const void* qkv, int in_dtype, long qkv_stride, c
                                const float* inv_freq, int rot_dims, void* q_out, void* k_cache, void* v_cache,
                                int out_dtype, const int* page_table, int max_blocks, int page_size,
                                const int* token_seq, const int* token_pos, const int* seq_slot, int n_tokens,
-                               int n_heads, int n_kv_heads, int head_dim, int v_dim, int write_kv,
+                               int n_heads, int n_kv_heads, int head_dim, int v_dim, int write_kv, int head_norm,
                                cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   CPI_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0,
@@ -449,8 +488,10 @@ extern "C" int cpi_qkv_prepare(const void* qkv, int in_dtype, long qkv_stride, c
               "qkv_prepare: %d rotated elements of a head of %d (an even number up to the head size)", rot_dims, head_dim);
   QkvPrepParams p{qkv, qkv_stride, bias, bias_dtype, q_norm, k_norm, norm_dtype, norm_whole, norm_eps, inv_freq,
                   rot_dims, q_out, k_cache, v_cache, page_table, max_blocks, page_size, token_seq, token_pos,
-                  seq_slot, n_heads, n_kv_heads, head_dim, v_dim, write_kv};
-  const size_t smem = (size_t)(n_heads + (write_kv ? n_kv_heads : 0)) * head_dim * sizeof(float);
+                  seq_slot, n_heads, n_kv_heads, head_dim, v_dim, write_kv, head_norm};
+  CPI_REQUIRE(!(head_norm && norm_whole), "qkv_prepare: a norm over the whole projection or one per head, not both");
+  const size_t row = (size_t)(n_heads + (write_kv ? n_kv_heads : 0)) * head_dim;
+  const size_t smem = (head_norm ? 2 * row + n_heads + n_kv_heads : row) * sizeof(float);
   CPI_REQUIRE(smem <= 200 * 1024, "qkv_prepare: a q and k row of %zu bytes does not fit in shared memory", smem);
   // with few tokens the blocks are large (a few elements per thread); a prompt has blocks enough
   const int threads = n_tokens <= 2 * sm_count() ? 1024 : 256;
@@ -473,7 +514,7 @@ extern "C" int cpi_attention_general(const void* q, void* out, const void* k_cac
                                      const int* token_seq, const int* token_pos, const int* seq_slot,
                                      int n_tokens, int n_heads, int n_kv_heads, int head_dim,
                                      int window_kind, int window_size, float scale, const float* score_bias,
-                                     int n_dist, const float* sink, int v_dim, cudaStream_t stream) {
+                                     int n_dist, const float* sink, int v_dim, int keep_first, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   CPI_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0,
               "attention: %d heads cannot be grouped over %d key/value heads", n_heads, n_kv_heads);
@@ -483,7 +524,8 @@ extern "C" int cpi_attention_general(const void* q, void* out, const void* k_cac
   CPI_REQUIRE(window_kind == 0 || window_size > 0, "attention: window kind %d needs a size > 0", window_kind);
   CPI_REQUIRE(n_heads <= 65535, "attention: too many heads (%d)", n_heads);
   AttnParams p{q, out, k_cache, v_cache, page_table, max_blocks, page_size, token_seq, token_pos, seq_slot,
-               n_heads, n_kv_heads, head_dim, window_kind, window_size, scale, score_bias, n_dist, sink, v_dim};
+               n_heads, n_kv_heads, head_dim, window_kind, window_size, scale, score_bias, n_dist, sink, v_dim,
+               window_kind == 2 && keep_first > 0 ? keep_first : 0};
   dim3 grid(n_tokens, n_heads);
   CPI_DISPATCH_DTYPE(dtype, T, cpi::launch_pdl(attention_general_kernel<T>, grid, ATT_NT, 0, stream, p));
   return check_launch("attention_general");

@@ -206,16 +206,72 @@ __device__ __forceinline__ float gate_act(float a, int act) {
   return a / (1.0f + expf(-a));
 }
 
+// act 2, the clamped form: g = min(gate, limit), u = clamp(up, -limit, limit), out = g * sigmoid(1.702 g) * (u + 1)
+__device__ __forceinline__ float clamped_gate_mul(float g, float u, float limit) {
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  return g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+}
+
 template <typename TI, typename T>
-__global__ void swiglu_kernel(const TI* __restrict__ gu, T* __restrict__ out, int inter, int act) {
+__global__ void swiglu_kernel(const TI* __restrict__ gu, T* __restrict__ out, int inter, int act, float limit) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
   const TI* g = gu + (size_t)t * 2 * inter;
   for (int i = threadIdx.x; i < inter; i += blockDim.x) {
     const float a = to_f32(g[i]), b = to_f32(g[inter + i]);
-    out[(size_t)t * inter + i] = from_f32<T>(gate_act(a, act) * b);
+    out[(size_t)t * inter + i] = from_f32<T>(act == 2 ? clamped_gate_mul(a, b, limit) : gate_act(a, act) * b);
   }
+}
+
+// Branches that are normalised before they are summed: out[t] (+)= scale * sum_b rmsnorm(y_b[t]) * w_b, each branch
+// by its own mean square over the row (float32 rows in, float32 out; weights of any dtype).
+constexpr int kMaxBranches = 4;
+struct BranchSumParams {
+  const float* y[kMaxBranches]; long y_stride[kMaxBranches]; const void* w[kMaxBranches];
+  int w_dtype, n_branches, width, add;
+  float eps, scale;
+  float* out; long out_stride;
+};
+
+__global__ void __launch_bounds__(256) branch_norm_sum_kernel(BranchSumParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[32];
+  const int t = blockIdx.x;
+  float inv[kMaxBranches];
+#pragma unroll
+  for (int b = 0; b < kMaxBranches; ++b) {
+    inv[b] = 0.f;
+    if (b < p.n_branches) {
+      const float* y = p.y[b] + (size_t)t * p.y_stride[b];
+      float ss = 0.f;
+      for (int i = threadIdx.x; i < p.width; i += blockDim.x) ss = fmaf(y[i], y[i], ss);
+      inv[b] = 1.0f / sqrtf(block_sum(ss, scratch) / (float)p.width + p.eps);
+    }
+  }
+  float* o = p.out + (size_t)t * p.out_stride;
+  for (int i = threadIdx.x; i < p.width; i += blockDim.x) {
+    float acc = 0.f;
+#pragma unroll
+    for (int b = 0; b < kMaxBranches; ++b)
+      if (b < p.n_branches) acc += p.y[b][(size_t)t * p.y_stride[b] + i] * inv[b] * load_any(p.w[b], p.w_dtype, i);
+    acc *= p.scale;
+    o[i] = p.add ? o[i] + acc : acc;
+  }
+}
+
+// out[t] = [a[t] | b[t]] in out's dtype: two float32 rows side by side as one operand row of a product
+template <typename TO>
+__global__ void __launch_bounds__(256) concat_rows_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                                                          TO* __restrict__ out, int wa, int wb) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  TO* o = out + (size_t)t * (wa + wb);
+  for (int i = threadIdx.x; i < wa + wb; i += blockDim.x)
+    o[i] = from_f32<TO>(i < wa ? a[(size_t)t * wa + i] : b[(size_t)t * wb + i - wa]);
 }
 
 // logits <- cap * tanh(logits * scale / cap), or logits * scale when cap is 0.
@@ -300,20 +356,21 @@ extern "C" int cpi_moe_combine(float* residual, const void* y, int y_dtype, cons
 
 extern "C" int cpi_swiglu(const void* gate_up, void* out, int dtype, int n_rows, int inter, cudaStream_t stream) {
   if (n_rows == 0) return 0;
-  CPI_DISPATCH_DTYPE(dtype, T, cpi::launch_pdl(swiglu_kernel<T, T>, n_rows, 256, 0, stream, (const T*)gate_up, (T*)out, inter, 0));
+  CPI_DISPATCH_DTYPE(dtype, T, cpi::launch_pdl(swiglu_kernel<T, T>, n_rows, 256, 0, stream, (const T*)gate_up, (T*)out, inter, 0, 0.f));
   return check_launch("swiglu");
 }
 
-// out = act(gate) * up for rows [gate | up] of float32 or of out's dtype; act 0 = silu, 1 = gelu (tanh form)
+// out = act(gate) * up for rows [gate | up] of float32 or of out's dtype; act 0 = silu, 1 = gelu (tanh form),
+// 2 = the clamped form min(g, limit) * sigmoid(1.702 min(g, limit)) * (clamp(u, -limit, limit) + 1)
 extern "C" int cpi_gated_act(const void* gate_up, int in_dtype, void* out, int out_dtype, int n_rows, int inter,
-                             int act, cudaStream_t stream) {
+                             int act, float limit, cudaStream_t stream) {
   if (n_rows == 0) return 0;
-  CPI_REQUIRE(act == 0 || act == 1, "gated_act: unknown activation %d", act);
+  CPI_REQUIRE(act >= 0 && act <= 2, "gated_act: unknown activation %d", act);
   if (in_dtype == kF32) {
-    CPI_DISPATCH_DTYPE(out_dtype, T, cpi::launch_pdl(swiglu_kernel<float, T>, n_rows, 256, 0, stream, (const float*)gate_up, (T*)out, inter, act));
+    CPI_DISPATCH_DTYPE(out_dtype, T, cpi::launch_pdl(swiglu_kernel<float, T>, n_rows, 256, 0, stream, (const float*)gate_up, (T*)out, inter, act, limit));
   } else {
     CPI_REQUIRE(in_dtype == out_dtype, "gated_act: bfloat16 rows give bfloat16 rows");
-    cpi::launch_pdl(swiglu_kernel<__nv_bfloat16, __nv_bfloat16>, n_rows, 256, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, act);
+    cpi::launch_pdl(swiglu_kernel<__nv_bfloat16, __nv_bfloat16>, n_rows, 256, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, act, limit);
   }
   return check_launch("gated_act");
 }
@@ -323,4 +380,24 @@ extern "C" int cpi_logit_post(float* logits, long n, float scale, float cap, cud
   const int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
   cpi::launch_pdl(logit_post_kernel, blocks, 256, 0, stream, logits, n, scale, cap);
   return check_launch("logit_post");
+}
+
+extern "C" int cpi_branch_norm_sum(const float* const* y, const long* y_stride, const void* const* w, int w_dtype,
+                                   int n_branches, int n_rows, int width, float eps, float scale, int add, float* out,
+                                   long out_stride, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  CPI_REQUIRE(n_branches >= 1 && n_branches <= kMaxBranches, "branch_norm_sum: %d branches (1 to %d)", n_branches, kMaxBranches);
+  BranchSumParams p{};
+  for (int b = 0; b < n_branches; ++b) { p.y[b] = y[b]; p.y_stride[b] = y_stride[b]; p.w[b] = w[b]; }
+  p.w_dtype = w_dtype; p.n_branches = n_branches; p.width = width; p.add = add; p.eps = eps; p.scale = scale;
+  p.out = out; p.out_stride = out_stride;
+  cpi::launch_pdl(branch_norm_sum_kernel, n_rows, 256, 0, stream, p);
+  return check_launch("branch_norm_sum");
+}
+
+extern "C" int cpi_concat_rows(const float* a, const float* b, void* out, int out_dtype, int n_rows, int wa, int wb,
+                               cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  CPI_DISPATCH_DTYPE(out_dtype, TO, cpi::launch_pdl(concat_rows_kernel<TO>, n_rows, 256, 0, stream, a, b, (TO*)out, wa, wb));
+  return check_launch("concat_rows");
 }

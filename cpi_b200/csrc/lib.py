@@ -20,7 +20,7 @@ WINDOW_KINDS = {"full": WINDOW_FULL, "chunk": WINDOW_CHUNK, "sliding": WINDOW_SL
 MAX_DECODE_SPLITS = 256          # key splits that the combine kernel of decode attention takes
 PREFILL_TILE_ROWS = 256          # most query rows of one sequence that a block of the prefill attention kernel takes
 
-ABI_VERSION = 2                  # what cpi_abi_version() of a matching library answers
+ABI_VERSION = 3                  # what cpi_abi_version() of a matching library answers
 
 _lib = None
 scratch_generation = 0    # grows whenever a scratch buffer of this module is (re)allocated
@@ -322,11 +322,12 @@ def qkv_post(qkv, q_out, k_cache, v_cache, page_table, page_size, token_seq, tok
 
 def attention_general(q, out, k_cache, v_cache, page_table, page_size, token_seq, token_pos, seq_slot, *,
                       n_heads, n_kv_heads, head_dim, window_kind, window_size, scale, score_bias=None, sink=None,
-                      value_dim=None):
+                      value_dim=None, keep_first=0):
     """Attention of any head size and dtype over the paged cache.  `score_bias`: float32 [heads, n_dist] added
     to the scaled scores, indexed by the distance query position - key position (the last column for longer).
     `sink`: float32 [heads]; exp(sink[h]) is one more term of the softmax denominator, without a key or a value.
-    `value_dim`: elements of a value row when it differs from the keys' `head_dim`."""
+    `value_dim`: elements of a value row when it differs from the keys' `head_dim`.  `keep_first`: with a sliding
+    window, a sequence's first positions that every later query still sees."""
     _need_cuda(q, out, k_cache, v_cache, page_table, token_seq, token_pos, seq_slot, score_bias, sink)
     assert q.is_contiguous() and out.is_contiguous() and q.dtype == out.dtype == k_cache.dtype == v_cache.dtype
     assert score_bias is None or (score_bias.dtype == torch.float32 and score_bias.is_contiguous()
@@ -339,15 +340,17 @@ def attention_general(q, out, k_cache, v_cache, page_table, page_size, token_seq
           _p(page_table), c_int(page_table.shape[1]), c_int(page_size), _p(token_seq), _p(token_pos),
           _p(seq_slot), c_int(T), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_int(window_kind),
           c_int(window_size), c_float(scale), _p(score_bias),
-          c_int(0 if score_bias is None else score_bias.shape[1]), _p(sink), c_int(value_dim), _stream())
+          c_int(0 if score_bias is None else score_bias.shape[1]), _p(sink), c_int(value_dim), c_int(int(keep_first)),
+          _stream())
 
 
 def qkv_prepare(qkv, q_out, k_cache, v_cache, page_table, page_size, token_seq, token_pos, seq_slot, *, n_heads,
                 n_kv_heads, head_dim, value_dim, bias=None, q_norm=None, k_norm=None, norm_whole=False, norm_eps=0.0,
-                inv_freq=None, rotary_dims=0, write_kv=True):
+                inv_freq=None, rotary_dims=0, write_kv=True, head_norm=False):
     """The general form of `qkv_post`, a block per token: rows [q | k | v] (float32 or the cache's dtype) get
     their bias, q and k an RMS norm over the whole projection (`norm_whole`, weights `q_norm` / `k_norm`), the
-    first `rotary_dims` elements of each head their rotation; q goes to q_out, k and v into the cache pages."""
+    first `rotary_dims` elements of each head their rotation, and then (`head_norm`) every q and k head a weightless
+    RMS norm with `norm_eps`; q goes to q_out, k and v into the cache pages."""
     _need_cuda(qkv, q_out, k_cache, v_cache, page_table, token_seq, token_pos, seq_slot, bias, q_norm, k_norm, inv_freq)
     _rowmajor(qkv, "qkv_prepare qkv")
     T = qkv.shape[0]
@@ -364,7 +367,7 @@ def qkv_prepare(qkv, q_out, k_cache, v_cache, page_table, page_size, token_seq, 
           _p(inv_freq), c_int(rotary_dims), _p(q_out), _p(k_cache), _p(v_cache), c_int(dtype_code(q_out.dtype)),
           _p(page_table), c_int(page_table.shape[1]), c_int(page_size), _p(token_seq), _p(token_pos), _p(seq_slot),
           c_int(T), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_int(value_dim), c_int(int(write_kv)),
-          _stream())
+          c_int(int(head_norm)), _stream())
 
 
 def hc_step(x, *, y=None, mix=None, write=None, read=None, rows=None, norm_weight=None, norm_offset=0.0, eps=0.0,
@@ -409,15 +412,18 @@ def causal_conv(x, weight, bias, carry, out, batch, *, silu=True):
 
 
 def linear_scan(k, q, v, state, out, batch, *, n_heads, heads_per_group, n_rows, n_cols, z=None, z_bias=None,
-                tau=1.0, dt=None, dt_bias=None, a_log=None, skip=None, q_scale=1.0, decay_ready=False):
+                tau=1.0, dt=None, dt_bias=None, a_log=None, skip=None, q_scale=1.0, decay_ready=False,
+                decay_kind=0, beta=None):
     """The recurrence S_t = diag(a_t) S_{t-1} + k_t v_t^T, o_t = S_t^T q_t (+ skip v_t) per sequence and head over the
     state [slots, heads, n_rows, n_cols] (float32, updated in place).  Give `z` [T, heads * n_rows] for a decay per
     row, a = sigmoid(z + z_bias)^(1 / tau); or `dt` [T, heads] for a decay per head with a step size,
     dt' = softplus(dt + dt_bias), a = exp(-exp(a_log) dt'), v' = dt' v.  All rows float32 (column slices allowed).
-    `decay_ready`: `z` already holds a (`row_decay` ran over it).  `q_scale` multiplies the outputs' S^T q."""
+    `decay_ready`: `z` already holds a (`row_decay` ran over it).  `q_scale` multiplies the outputs' S^T q.
+    `decay_kind` 1 (with `z` and `a_log`): a = exp(-exp(a_log[head]) softplus(z + z_bias)).  `beta` [T, heads]
+    (before its sigmoid, with `z`): the delta rule, after the decay u = sigmoid(beta) (v - S^T k), S += k u^T."""
     small = [t for t in (z_bias, dt_bias, a_log, skip) if t is not None]
-    _need_cuda(k, q, v, state, out, z, dt, *small)
-    for t in (k, q, v, out, z, dt):
+    _need_cuda(k, q, v, state, out, z, dt, beta, *small)
+    for t in (k, q, v, out, z, dt, beta):
         assert t is None or (t.dtype == torch.float32 and t.dim() == 2 and t.stride(1) == 1)
     assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (n_heads, n_rows, n_cols)
     sd = small[0].dtype if small else torch.float32
@@ -427,23 +433,28 @@ def linear_scan(k, q, v, state, out, batch, *, n_heads, heads_per_group, n_rows,
           _p(dt), c_long(0 if dt is None else dt.stride(0)), _p(dt_bias), _p(a_log), _p(skip), c_int(dtype_code(sd)),
           c_float(q_scale), _p(state), _p(out), c_long(out.stride(0)), _p(batch.seq_slot), _p(batch.seq_tok0),
           _p(batch.seq_new), c_int(batch.n_seqs), c_int(getattr(batch, "max_new", 1 << 20)), c_int(n_heads),
-          c_int(heads_per_group), c_int(n_rows), c_int(n_cols), c_int(int(decay_ready)),
-          _stream())
+          c_int(heads_per_group), c_int(n_rows), c_int(n_cols), c_int(int(decay_ready)), c_int(int(decay_kind)),
+          _p(beta), c_long(0 if beta is None else beta.stride(0)), _stream())
 
 
-def row_decay(z, z_bias, tau):
+def row_decay(z, z_bias, tau, *, kind=0, a_log=None, rows_per_head=0):
     """z <- sigmoid(z + z_bias)^(1 / tau) in place, z [T, n] float32 rows: the decays of `linear_scan`'s row flavour,
     prepared once per element for a step of many tokens (the recurrence computes the same expression itself when
-    it is not given them)."""
-    _need_cuda(z, z_bias)
+    it is not given them).  kind 1: z <- exp(-exp(a_log[i // rows_per_head]) softplus(z + z_bias)); `a_log` has
+    `z_bias`'s dtype."""
+    _need_cuda(z, z_bias, a_log)
+    assert a_log is None or (z_bias is not None and a_log.dtype == z_bias.dtype and a_log.is_contiguous())
     assert z.dtype == torch.float32 and z.dim() == 2 and z.stride(1) == 1
     assert z_bias is None or (z_bias.is_contiguous() and z_bias.numel() == z.shape[1])
     _call("cpi_row_decay", _p(z), c_long(z.stride(0)), _p(z_bias),
           c_int(F32 if z_bias is None else dtype_code(z_bias.dtype)), c_float(1.0 / float(tau)), c_int(z.shape[0]),
-          c_int(z.shape[1]), _stream())
+          c_int(z.shape[1]), c_int(int(kind)), _p(a_log), c_int(int(rows_per_head)), _stream())
 
 
-def gated_norm(y, gate, weight, out, *, parts, gate_first, eps):
+GATE_NORM_ACTS = {"silu": 0, "sigmoid": 1}
+
+
+def gated_norm(y, gate, weight, out, *, parts, gate_first, eps, gate_act="silu"):
     """out = norm(y * silu(gate)) * weight (gate_first) or norm(y) * weight * silu(gate): an RMS norm over each of
     `parts` equal pieces of a row by its own mean square; weight index = element % len(weight).  y, gate float32."""
     _need_cuda(y, gate, weight, out)
@@ -454,19 +465,55 @@ def gated_norm(y, gate, weight, out, *, parts, gate_first, eps):
     _call("cpi_gated_norm", _p(y), c_long(y.stride(0)), _p(gate), c_long(0 if gate is None else gate.stride(0)),
           _p(weight), c_int(F32 if weight is None else dtype_code(weight.dtype)),
           c_int(0 if weight is None else weight.numel()), _p(out), c_int(dtype_code(out.dtype)), c_long(out.stride(0)),
-          c_int(T), c_int(W), c_int(parts), c_int(int(gate_first)), c_float(eps), _stream())
+          c_int(T), c_int(W), c_int(parts), c_int(int(gate_first)), c_float(eps), c_int(GATE_NORM_ACTS[gate_act]),
+          _stream())
 
 
-GATE_ACTS = {"silu": 0, "gelu_tanh": 1}
+GATE_ACTS = {"silu": 0, "gelu_tanh": 1, "swish_clamped": 2}
 
 
-def gated_act(gate_up, out, act: str):
-    """out = act(gate) * up for rows [gate | up] (float32, or out's dtype)."""
+def gated_act(gate_up, out, act: str, limit: float = 0.0):
+    """out = act(gate) * up for rows [gate | up] (float32, or out's dtype); "swish_clamped" is
+    g sigmoid(1.702 g) (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit)."""
     _need_cuda(gate_up, out)
     T, I = out.shape
     assert gate_up.shape == (T, 2 * I) and gate_up.is_contiguous() and out.is_contiguous()
     _call("cpi_gated_act", _p(gate_up), c_int(dtype_code(gate_up.dtype)), _p(out), c_int(dtype_code(out.dtype)),
-          c_int(T), c_int(I), c_int(GATE_ACTS[act]), _stream())
+          c_int(T), c_int(I), c_int(GATE_ACTS[act]), c_float(limit), _stream())
+
+
+def head_unit(x, *, heads, dim, eps):
+    """x[t, head, :] <- x / sqrt(sum(x^2) + eps) in place: float32 rows (a column slice allowed) of `heads` heads."""
+    _need_cuda(x)
+    assert x.dtype == torch.float32 and x.dim() == 2 and x.stride(1) == 1 and x.shape[1] == heads * dim
+    _call("cpi_head_unit", _p(x), c_long(x.stride(0)), c_int(x.shape[0]), c_int(heads), c_int(dim), c_float(eps), _stream())
+
+
+def branch_norm_sum(branches, weights, out, *, eps, scale=1.0, add=False):
+    """out (+)= scale * sum_b rmsnorm(branches[b]) * weights[b]: up to four float32 [T, W] branches, each divided by
+    its own root mean square over the row; weights [W] of one dtype; out float32 [T, W]."""
+    _need_cuda(out, *branches, *weights)
+    n = len(branches)
+    T, W = out.shape
+    assert 1 <= n <= 4 and len(weights) == n and out.dtype == torch.float32 and out.stride(1) == 1
+    for y, w in zip(branches, weights):
+        assert y.dtype == torch.float32 and y.shape == (T, W) and y.stride(1) == 1
+        assert w.is_contiguous() and w.numel() == W and w.dtype == weights[0].dtype
+    ys = (c_void_p * n)(*[y.data_ptr() for y in branches])
+    st = (c_long * n)(*[y.stride(0) for y in branches])
+    ws = (c_void_p * n)(*[w.data_ptr() for w in weights])
+    _call("cpi_branch_norm_sum", ys, st, ws, c_int(dtype_code(weights[0].dtype)), c_int(n), c_int(T), c_int(W),
+          c_float(eps), c_float(scale), c_int(int(add)), _p(out), c_long(out.stride(0)), _stream())
+
+
+def concat_rows(a, b, out):
+    """out[t] = [a[t] | b[t]] in out's dtype; a, b contiguous float32 [T, *]."""
+    _need_cuda(a, b, out)
+    T = a.shape[0]
+    assert a.dtype == torch.float32 and b.dtype == torch.float32 and a.is_contiguous() and b.is_contiguous()
+    assert out.is_contiguous() and out.shape == (T, a.shape[1] + b.shape[1]) and b.shape[0] == T
+    _call("cpi_concat_rows", _p(a), _p(b), _p(out), c_int(dtype_code(out.dtype)), c_int(T), c_int(a.shape[1]),
+          c_int(b.shape[1]), _stream())
 
 
 def logit_post(logits, scale: float, softcap: float):
@@ -535,8 +582,17 @@ def attention_prefill(q, out, k_cache, v_cache, page_table, page_size, token_seq
           _p(sink), _stream())
 
 
-def router_topk(h, w, topk_idx, topk_gate, *, top_k, sigmoid_gate, logits_out=None):
-    _need_cuda(h, w, topk_idx, topk_gate, logits_out)
+ROUTER_GATES = {"none": 0, "sigmoid": 1, "softmax_chosen": 2}
+
+
+def _gate_mode(sigmoid_gate) -> int:
+    """False / True (the older spelling: no gate / sigmoid of the chosen logit) or a name of ROUTER_GATES."""
+    return ROUTER_GATES[sigmoid_gate] if isinstance(sigmoid_gate, str) else int(bool(sigmoid_gate))
+
+
+def router_topk(h, w, topk_idx, topk_gate, *, top_k, sigmoid_gate, logits_out=None, bias=None):
+    _need_cuda(h, w, topk_idx, topk_gate, logits_out, bias)
+    assert bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == w.shape[0])
     _rowmajor(h, "router h")
     T, H = h.shape
     E = w.shape[0]
@@ -549,16 +605,18 @@ def router_topk(h, w, topk_idx, topk_gate, *, top_k, sigmoid_gate, logits_out=No
         n = min(65535, T - t0)
         _call("cpi_router_topk", _p(h[t0:t0 + n]), c_int(dtype_code(h.dtype)), c_long(h.stride(0)), _p(w),
               c_int(dtype_code(w.dtype)), _p(logits_out[t0:t0 + n]), _p(topk_idx[t0:t0 + n]), _p(topk_gate[t0:t0 + n]),
-              c_int(n), c_int(H), c_int(E), c_int(top_k), c_int(int(sigmoid_gate)), _stream())
+              c_int(n), c_int(H), c_int(E), c_int(top_k), c_int(_gate_mode(sigmoid_gate)), _p(bias), _stream())
 
 
 def moe_route(h, w, topk_idx, topk_gate, logits, group_offsets, row_token, row_scale, row_of_slot, *, top_k,
-              sigmoid_gate, sorted_h=None) -> bool:
+              sigmoid_gate, sorted_h=None, bias=None) -> bool:
     """Router logits, the top-k choice and the per-expert row lists of a step; returns whether
     `sorted_h` (the activation rows in expert order) was filled too.  A step with few tokens takes two
     launches (logits, then one kernel for the rest), a larger one the separate kernels; the results
-    are the same."""
-    _need_cuda(h, w, topk_idx, topk_gate, logits, group_offsets, row_token, row_scale, row_of_slot, sorted_h)
+    are the same.  `sigmoid_gate`: False, True or a name of ROUTER_GATES; `bias`: float32 [experts] added to the logits."""
+    _need_cuda(h, w, topk_idx, topk_gate, logits, group_offsets, row_token, row_scale, row_of_slot, sorted_h, bias)
+    assert bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == w.shape[0])
+    gm = _gate_mode(sigmoid_gate)
     _rowmajor(h, "router h")
     T, H = h.shape
     E = w.shape[0]
@@ -566,8 +624,8 @@ def moe_route(h, w, topk_idx, topk_gate, logits, group_offsets, row_token, row_s
         assert w.is_contiguous() and w.shape[1] == H and logits.dtype == torch.float32 and logits.is_contiguous()
         _call("cpi_router_topk", _p(h), c_int(dtype_code(h.dtype)), c_long(h.stride(0)), _p(w),
               c_int(dtype_code(w.dtype)), _p(logits), None, None, c_int(T), c_int(H), c_int(E), c_int(top_k),
-              c_int(int(sigmoid_gate)), _stream())
-        rc = load().cpi_moe_route_small(_p(logits), c_int(T), c_int(E), c_int(top_k), c_int(int(sigmoid_gate)),
+              c_int(gm), _p(bias), _stream())
+        rc = load().cpi_moe_route_small(_p(logits), c_int(T), c_int(E), c_int(top_k), c_int(gm),
                                         _p(topk_idx), _p(topk_gate), _p(group_offsets), _p(row_token), _p(row_scale),
                                         _p(row_of_slot), _p(h), c_long(h.stride(0) * h.element_size()), _p(sorted_h),
                                         c_int(H * h.element_size()), _stream())
@@ -579,9 +637,9 @@ def moe_route(h, w, topk_idx, topk_gate, logits, group_offsets, row_token, row_s
             raise KernelError(load().cpi_last_error().decode())
         # too large or unaligned for the one-launch kernel: select here, lists below
         _call("cpi_router_select", _p(logits), _p(topk_idx), _p(topk_gate), c_int(T), c_int(E), c_int(top_k),
-              c_int(int(sigmoid_gate)), _stream())
+              c_int(gm), _stream())
     else:
-        router_topk(h, w, topk_idx, topk_gate, top_k=top_k, sigmoid_gate=sigmoid_gate, logits_out=logits)
+        router_topk(h, w, topk_idx, topk_gate, top_k=top_k, sigmoid_gate=sigmoid_gate, logits_out=logits, bias=bias)
     moe_lists(topk_idx, topk_gate, group_offsets, row_token, row_scale, row_of_slot, n_tokens=T, top_k=top_k,
               n_experts=E)
     return False

@@ -3,7 +3,8 @@
 // Reference: router logits = W_r h, the single best expert by a strict '>' scanning upward, so ties go
 // to the lowest index, and no gate value (src/engine/llama4_cpu_engine.cpp:256-263; on the host in its
 // CUDA engine, src/engine/llama4_cuda_engine_setup.cu:488-519).  Top-k > 1 and the gate
-// g = 1 / (1 + exp(-logit)) are this library's own.  Router math is float32 whatever the activation
+// g = 1 / (1 + exp(-logit)) are this library's own, as are a bias on the logits and gates that are the softmax
+// over the chosen logits.  Router math is float32 whatever the activation
 // dtype, each logit summed in a fixed order so that a token's choice does not depend on its batch.
 #include "common.cuh"
 
@@ -37,7 +38,7 @@ template <typename T> __device__ __forceinline__ void load_group(const T* row, i
 template <typename TH, typename TW>
 __global__ void __launch_bounds__(128)
 router_logits_kernel(const TH* __restrict__ h, long h_stride, const TW* __restrict__ w,
-                     float* __restrict__ logits, int hidden, int n_experts, int vec) {
+                     float* __restrict__ logits, int hidden, int n_experts, int vec, const float* __restrict__ bias) {
   pdl_launch_dependents();
   __shared__ float scratch[32];
   const int e = blockIdx.x, t = blockIdx.y;
@@ -76,7 +77,7 @@ router_logits_kernel(const TH* __restrict__ h, long h_stride, const TW* __restri
     }
   }
   s = block_sum(s, scratch);
-  if (threadIdx.x == 0) logits[(size_t)t * n_experts + e] = s;
+  if (threadIdx.x == 0) logits[(size_t)t * n_experts + e] = bias ? s + bias[e] : s;
 }
 
 // A block takes TOK tokens and EXP experts at a time -- for many tokens: every loaded activation is used
@@ -84,7 +85,8 @@ router_logits_kernel(const TH* __restrict__ h, long h_stride, const TW* __restri
 template <typename TH, typename TW, int TOK, int EXP>
 __global__ void __launch_bounds__(128)
 router_logits_tile_kernel(const TH* __restrict__ h, long h_stride, const TW* __restrict__ w,
-                          float* __restrict__ logits, int n_tokens, int hidden, int n_experts, int vec) {
+                          float* __restrict__ logits, int n_tokens, int hidden, int n_experts, int vec,
+                          const float* __restrict__ bias) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float part[4][TOK * EXP];
@@ -124,12 +126,13 @@ router_logits_tile_kernel(const TH* __restrict__ h, long h_stride, const TW* __r
     if (t0 + a < n_tokens && e0 + b < n_experts) {
       float r = 0.f;
       for (int wq = 0; wq < 4; ++wq) r += part[wq][k];
-      logits[(size_t)(t0 + a) * n_experts + e0 + b] = r;
+      logits[(size_t)(t0 + a) * n_experts + e0 + b] = bias ? r + bias[e0 + b] : r;
     }
   }
 }
 
-// The k best logits of one token, ties to the lowest index; gate = sigmoid of the chosen logit.
+// The k best logits of one token, ties to the lowest index; gate = 1 (mode 0), the sigmoid of the chosen logit
+// (mode 1), or the softmax over the chosen logits (mode 2).
 __device__ __forceinline__ void select_topk(const float* lg, int* idx, float* gate, int n_experts, int top_k, int gate_mode) {
   for (int k = 0; k < top_k; ++k) {
     int best = -1;
@@ -151,7 +154,14 @@ __device__ __forceinline__ void select_topk(const float* lg, int* idx, float* ga
       bv = lg[best];
     }
     idx[k] = best;
-    gate[k] = gate_mode == 0 ? 1.0f : 1.0f / (1.0f + expf(-bv));
+    gate[k] = gate_mode == 0 ? 1.0f : gate_mode == 2 ? bv : 1.0f / (1.0f + expf(-bv));
+  }
+  if (gate_mode == 2) {                             // the first chosen logit is the largest
+    const float top = gate[0];
+    float sum = 0.f;
+    for (int k = 0; k < top_k; ++k) { gate[k] = expf(gate[k] - top); sum += gate[k]; }
+    const float inv = 1.0f / sum;
+    for (int k = 0; k < top_k; ++k) gate[k] *= inv;
   }
 }
 
@@ -288,12 +298,13 @@ moe_lists_kernel(const int* __restrict__ topk_idx, const float* __restrict__ top
 
 using namespace cpi;
 
-// gate_mode: 0 none (gates are 1), 1 sigmoid of the chosen logit
-// gate_mode: 0 none (gates are 1), 1 sigmoid of the chosen logit.  `logits` is float32 [n_tokens, n_experts]
-// scratch that also serves as the optional output of the router logits.
+// gate_mode: 0 none (gates are 1), 1 sigmoid of the chosen logit, 2 softmax over the chosen logits.  `logits` is
+// float32 [n_tokens, n_experts] scratch that also serves as the optional output of the router logits; `bias`
+// (float32 [n_experts] or null) is added to them.
 extern "C" int cpi_router_topk(const void* h, int h_dtype, long h_stride, const void* w, int w_dtype,
                                float* logits, int* topk_idx, float* topk_gate, int n_tokens,
-                               int hidden, int n_experts, int top_k, int gate_mode, cudaStream_t stream) {
+                               int hidden, int n_experts, int top_k, int gate_mode, const float* bias,
+                               cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   CPI_REQUIRE(n_experts >= 1 && n_experts <= kMaxExperts, "router: %d experts (supported: 1..%d)", n_experts, kMaxExperts);
   CPI_REQUIRE(top_k >= 1 && top_k <= n_experts, "router: top-k %d of %d experts", top_k, n_experts);
@@ -306,11 +317,11 @@ extern "C" int cpi_router_topk(const void* h, int h_dtype, long h_stride, const 
     constexpr int TOK = 4, EXP = 4;
     dim3 grid((n_tokens + TOK - 1) / TOK, (n_experts + EXP - 1) / EXP);
     CPI_DISPATCH_DTYPE(h_dtype, TH, CPI_DISPATCH_DTYPE(w_dtype, TW,
-        (cpi::launch_pdl(router_logits_tile_kernel<TH, TW, TOK, EXP>, grid, 128, 0, stream, (const TH*)h, h_stride, (const TW*)w, logits, n_tokens, hidden, n_experts, vec))));
+        (cpi::launch_pdl(router_logits_tile_kernel<TH, TW, TOK, EXP>, grid, 128, 0, stream, (const TH*)h, h_stride, (const TW*)w, logits, n_tokens, hidden, n_experts, vec, bias))));
   } else {
     dim3 grid(n_experts, n_tokens);
     CPI_DISPATCH_DTYPE(h_dtype, TH, CPI_DISPATCH_DTYPE(w_dtype, TW,
-        (cpi::launch_pdl(router_logits_kernel<TH, TW>, grid, 128, 0, stream, (const TH*)h, h_stride, (const TW*)w, logits, hidden, n_experts, vec))));
+        (cpi::launch_pdl(router_logits_kernel<TH, TW>, grid, 128, 0, stream, (const TH*)h, h_stride, (const TW*)w, logits, hidden, n_experts, vec, bias))));
   }
   if (check_launch("router_logits")) return 2;
   if (!topk_idx) return 0;                          // logits only: the caller selects in a later kernel

@@ -12,8 +12,12 @@
 //                      dt = softplus(raw_t + dt_bias), a_t = exp(-exp(A_log) dt), v_t' = dt v_t (the selective
 //                      state-space form, where k is called B, q is called C and heads share B and C in groups).
 //                      Decays, step sizes and the state are float32 whatever the activations are.
-//   gated_norm         out = norm_g(y * silu(g)) * w  or  norm_g(y) * w * silu(g): an RMS norm over equal parts
-//                      of a row (each part by its own mean square), gate before or after.
+//                      A row decay may also be a_t = exp(-exp(A_log[head]) * softplus(z_t + bias)).  With `beta`
+//                      the update is the delta rule: after the decay, u_t = beta_t (v_t - S^T k_t), S += k_t u_t^T,
+//                      o_t = S^T q_t (the read-out sees the token's own write).
+//   head_unit          rows of heads made unit vectors in place: x / sqrt(sum(x^2) + eps) per head.
+//   gated_norm         out = norm_g(y * act(g)) * w  or  norm_g(y) * w * act(g): an RMS norm over equal parts
+//                      of a row (each part by its own mean square), gate before or after; act is silu or sigmoid.
 //
 // A sequence's tokens are visited in order by one block per (sequence, head, slice of columns) with the same
 // arithmetic whether they come in one step or one at a time, so results do not depend on how a prompt is cut.
@@ -94,15 +98,24 @@ struct ScanParams {
   int chunk;                             // tokens staged in shared memory at a time
   int vec16;                             // the rows of k, q and z start on 16-byte boundaries and N is a multiple of 4
   int decay_ready;                       // z already holds the decays a (row_decay ran over it)
+  int decay_kind;                        // row flavour: 0 a = sigmoid(z + b)^(1/tau), 1 a = exp(-exp(a_log[head]) softplus(z + b))
+  const float* beta; long beta_stride;   // [T, H] before the sigmoid, or null; with it the update is the delta rule
 };
 
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
 __device__ __forceinline__ float log_sigmoid_f(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 // a = sigmoid(z + b)^(1 / tau); one function for the kernel that prepares a prompt's decays and for the recurrence
 // that computes a decoded token's own, so that both give the same bits
-__device__ __forceinline__ float row_decay_f(float z, float b, float inv_tau) { return expf(log_sigmoid_f(z + b) * inv_tau); }
+// (kind 1: a = exp(-rate * softplus(z + b)), rate = exp(A_log) of the row's head)
+__device__ __forceinline__ float row_decay_f(float z, float b, float inv_tau, int kind = 0, float rate = 0.f) {
+  if (kind == 1) return expf(-rate * softplus_f(z + b));
+  return expf(log_sigmoid_f(z + b) * inv_tau);
+}
 
-struct RowDecayParams { float* z; long z_stride; const void* bias; int bias_dtype; float inv_tau; int n; };
+struct RowDecayParams {
+  float* z; long z_stride; const void* bias; int bias_dtype; float inv_tau; int n;
+  int kind; const void* a_log; int rows_per_head;       // kind 1: element i belongs to head i / rows_per_head
+};
 
 // z[t, i] <- sigmoid(z[t, i] + bias[i])^(1 / tau), in place: the decays of a step of many tokens, once per element
 // instead of once per block of columns inside the recurrence
@@ -112,7 +125,8 @@ __global__ void __launch_bounds__(256) row_decay_kernel(RowDecayParams p) {
   const int i = blockIdx.y * blockDim.x + threadIdx.x;
   if (i >= p.n) return;
   float* z = p.z + (size_t)blockIdx.x * p.z_stride + i;
-  *z = row_decay_f(*z, p.bias ? load_any(p.bias, p.bias_dtype, i) : 0.f, p.inv_tau);
+  const float rate = p.kind == 1 ? expf(load_any(p.a_log, p.bias_dtype, i / p.rows_per_head)) : 0.f;
+  *z = row_decay_f(*z, p.bias ? load_any(p.bias, p.bias_dtype, i) : 0.f, p.inv_tau, p.kind, rate);
 }
 
 __device__ __forceinline__ void cp_async4(float* dst_smem, const float* src) {
@@ -132,7 +146,7 @@ template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile(
 // copied into what the recurrence needs (a = sigmoid(z + b)^(1/tau) unless the caller prepared it, or the step
 // size and the head's decay); q's constant scale multiplies the output sum.  Per token the rows' k, q and a lie as each lane group's NPT values followed by four words of padding,
 // so that the 16-byte reads of different kk fall into different banks.
-template <int NPT, int KS, bool ROW_DECAY, int CPT>
+template <int NPT, int KS, bool ROW_DECAY, int CPT, bool DELTA>
 __global__ void __launch_bounds__(256) linear_scan_kernel(ScanParams p) {
   pdl_launch_dependents();
   extern __shared__ __align__(16) float smem[];
@@ -155,7 +169,8 @@ __global__ void __launch_bounds__(256) linear_scan_kernel(ScanParams p) {
 
   // what no kernel writes comes before the wait: the head's constants, the bias; the buffers start as zeros
   // (rows past the state's size and columns past the head's are never copied into and stay zero)
-  float head_a = 0.f, head_dtb = 0.f, head_skip = 0.f;
+  float head_a = 0.f, head_dtb = 0.f, head_skip = 0.f, head_rate = 0.f;
+  if (ROW_DECAY && p.decay_kind == 1) head_rate = expf(load_any(p.a_log, p.small_dtype, h));
   if (!ROW_DECAY) {
     head_a = -expf(load_any(p.a_log, p.small_dtype, h));
     head_dtb = p.dt_bias ? load_any(p.dt_bias, p.small_dtype, h) : 0.f;
@@ -216,6 +231,10 @@ __global__ void __launch_bounds__(256) linear_scan_kernel(ScanParams p) {
       float* dts = dt_of(b);
       for (int j = tid; j < nc; j += blockDim.x) cp_async4(dts + j, p.dt + (size_t)(tok0 + c0 + j) * p.dt_stride + h);
     }
+    if (DELTA) {                                             // the place of the step sizes holds the write strengths
+      float* bs = dt_of(b);
+      for (int j = tid; j < nc; j += blockDim.x) cp_async4(bs + j, p.beta + (size_t)(tok0 + c0 + j) * p.beta_stride + h);
+    }
   };
 
   if (n_tok > 0) issue(0, smem);
@@ -236,9 +255,11 @@ __global__ void __launch_bounds__(256) linear_scan_kernel(ScanParams p) {
         const int j = e / (KS * NPT), n = e % (KS * NPT);
         if (n >= N) continue;
         const int at = j * ROWP + (n / NPT) * (NPT + 4) + n % NPT;
-        ds[at] = row_decay_f(ds[at], bias_s[n], p.inv_tau);
+        ds[at] = row_decay_f(ds[at], bias_s[n], p.inv_tau, p.decay_kind, head_rate);
       }
     }
+    if (DELTA)
+      for (int j = tid; j < nc; j += blockDim.x) dts[j] = 1.0f / (1.0f + expf(-dts[j]));
     if (!ROW_DECAY) {
       for (int j = tid; j < nc; j += blockDim.x) {
         const float dt = softplus_f(dts[j] + head_dtb);
@@ -246,7 +267,7 @@ __global__ void __launch_bounds__(256) linear_scan_kernel(ScanParams p) {
         as[j] = expf(head_a * dt);
       }
     }
-    if (transform) __syncthreads();
+    if (transform || DELTA) __syncthreads();
 #pragma unroll 2
     for (int j = 0; j < nc; ++j) {
       const float4* k4 = reinterpret_cast<const float4*>(ks + j * ROWP + kk * (NPT + 4));
@@ -262,6 +283,51 @@ __global__ void __launch_bounds__(256) linear_scan_kernel(ScanParams p) {
         vv[c] = make_float2(v_raw[c] * dtj, v_raw[c] * dtj);
         o2[c] = make_float2(0.f, 0.f);
       }
+      if constexpr (DELTA) {
+        // the delta rule: decay, then what the state already answers to this key, then the corrected write
+        float2 d2[CPT];
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) d2[c] = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int i4 = 0; i4 < NPT / 4; ++i4) {
+          const float4 kq = k4[i4];
+          float4 dd = make_float4(a, a, a, a);
+          if (ROW_DECAY) dd = d4[i4];
+          const float2 kr[2] = {make_float2(kq.x, kq.y), make_float2(kq.z, kq.w)};
+          const float2 dr[2] = {make_float2(dd.x, dd.y), make_float2(dd.z, dd.w)};
+#pragma unroll
+          for (int r = 0; r < 2; ++r) {
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) {
+              S[2 * i4 + r][c] = __fmul2_rn(dr[r], S[2 * i4 + r][c]);
+              d2[c] = __ffma2_rn(S[2 * i4 + r][c], kr[r], d2[c]);
+            }
+          }
+        }
+        const float beta = dts[j];
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) {
+          float d = d2[c].x + d2[c].y;
+#pragma unroll
+          for (int off = PVW; off < 32; off <<= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
+          const float u = beta * (v_raw[c] - d);
+          vv[c] = make_float2(u, u);
+        }
+#pragma unroll
+        for (int i4 = 0; i4 < NPT / 4; ++i4) {
+          const float4 kq = k4[i4], qq = q4[i4];
+          const float2 kr[2] = {make_float2(kq.x, kq.y), make_float2(kq.z, kq.w)};
+          const float2 qr[2] = {make_float2(qq.x, qq.y), make_float2(qq.z, qq.w)};
+#pragma unroll
+          for (int r = 0; r < 2; ++r) {
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) {
+              S[2 * i4 + r][c] = __ffma2_rn(kr[r], vv[c], S[2 * i4 + r][c]);
+              o2[c] = __ffma2_rn(S[2 * i4 + r][c], qr[r], o2[c]);
+            }
+          }
+        }
+      } else {
       // a thread's rows times its columns: k, q and the decay of a row are read once for all its columns
 #pragma unroll
       for (int i4 = 0; i4 < NPT / 4; ++i4) {
@@ -279,6 +345,7 @@ __global__ void __launch_bounds__(256) linear_scan_kernel(ScanParams p) {
             o2[c] = __ffma2_rn(S[2 * i4 + r][c], qr[r], o2[c]);
           }
         }
+      }
       }
 #pragma unroll
       for (int c = 0; c < CPT; ++c) {
@@ -308,7 +375,10 @@ struct GatedNormParams {
   const void* w; int w_dtype; int w_len; // weight index = i % w_len (a weight shared by all parts, or one per element)
   void* out; long out_stride;
   int width, parts, gate_first; float eps;
+  int gate_act;                          // 0 silu, 1 sigmoid
 };
+
+__device__ __forceinline__ float gate_f(float z, int act) { return act == 1 ? 1.0f / (1.0f + expf(-z)) : silu_f(z); }
 
 template <typename TO>
 __global__ void __launch_bounds__(128) gated_norm_kernel(GatedNormParams p) {
@@ -321,7 +391,7 @@ __global__ void __launch_bounds__(128) gated_norm_kernel(GatedNormParams p) {
   float ss = 0.f;
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
     float v = y[i];
-    if (g && p.gate_first) v *= silu_f(g[i]);
+    if (g && p.gate_first) v *= gate_f(g[i], p.gate_act);
     ss = fmaf(v, v, ss);
   }
   ss = block_sum(ss, scratch);
@@ -329,12 +399,25 @@ __global__ void __launch_bounds__(128) gated_norm_kernel(GatedNormParams p) {
   TO* o = reinterpret_cast<TO*>(p.out) + (size_t)t * p.out_stride + (size_t)part * n;
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
     float v = y[i];
-    if (g && p.gate_first) v *= silu_f(g[i]);
+    if (g && p.gate_first) v *= gate_f(g[i], p.gate_act);
     v *= inv;
     if (p.w) v *= load_any(p.w, p.w_dtype, (size_t)(part * n + i) % p.w_len);
-    if (g && !p.gate_first) v *= silu_f(g[i]);
+    if (g && !p.gate_first) v *= gate_f(g[i], p.gate_act);
     o[i] = from_f32<TO>(v);
   }
+}
+
+// x[t, head, :] <- x / sqrt(sum(x^2) + eps) in place, float32 rows of `heads` heads of `dim` elements; a warp per head
+__global__ void __launch_bounds__(128) head_unit_kernel(float* x, long stride, int heads, int dim, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int head = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (head >= heads) return;
+  float* r = x + (size_t)blockIdx.x * stride + (size_t)head * dim;
+  float ss = 0.f;
+  for (int i = lane; i < dim; i += 32) ss = fmaf(r[i], r[i], ss);
+  const float inv = 1.0f / sqrtf(warp_sum(ss) + eps);
+  for (int i = lane; i < dim; i += 32) r[i] *= inv;
 }
 
 template <int NPT, int KS, bool ROW, int CPT = 1>
@@ -354,14 +437,14 @@ static int launch_scan(const ScanParams& p0, int n_seqs, int max_new, int max_wa
   const size_t smem = ((size_t)2 * per_buf + KS * NPT) * sizeof(float);
   auto aligned = [](const float* q, long stride) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0 && stride % 4 == 0; };
   p.vec16 = p.n_rows % 4 == 0 && aligned(p.k, p.k_stride) && aligned(p.q, p.q_stride) && (!ROW || aligned(p.z, p.z_stride));
-  auto kern = linear_scan_kernel<NPT, KS, ROW, CPT>;
-  static bool attr_set = false;                              // per instantiation
-  if (smem > 48 * 1024 && !attr_set) {
+  auto kern = ROW && p.beta ? linear_scan_kernel<NPT, KS, ROW, CPT, ROW> : linear_scan_kernel<NPT, KS, ROW, CPT, false>;
+  static bool attr_set[2] = {false, false};                  // per instantiation
+  if (smem > 48 * 1024 && !attr_set[p.beta != nullptr]) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) {
       set_error("linear_scan: %zu bytes of shared memory were refused", smem);
       return 1;
     }
-    attr_set = true;
+    attr_set[p.beta != nullptr] = true;
   }
   dim3 grid(n_seqs, p.n_heads, (p.n_cols + pvb - 1) / pvb);
   cpi::launch_pdl(kern, grid, dim3(32 * nwarps), smem, stream, p);
@@ -436,37 +519,50 @@ extern "C" int cpi_linear_scan(const float* k, long k_stride, const float* q, lo
                                const void* skip, int small_dtype, float q_scale, float* state, float* out,
                                long out_stride, const int* seq_slot, const int* seq_tok0, const int* seq_new,
                                int n_seqs, int max_new, int n_heads, int heads_per_group, int n_rows, int n_cols,
-                               int decay_ready, cudaStream_t stream) {
+                               int decay_ready, int decay_kind, const float* beta, long beta_stride,
+                               cudaStream_t stream) {
   if (n_seqs == 0) return 0;
   CPI_REQUIRE((z != nullptr) != (dt != nullptr), "linear_scan: give row decays or step sizes, one of the two");
   CPI_REQUIRE(dt == nullptr || a_log != nullptr, "linear_scan: step sizes need the heads' decay rates");
   CPI_REQUIRE(n_heads > 0 && heads_per_group > 0 && n_heads % heads_per_group == 0 && n_rows > 0 && n_cols > 0,
               "linear_scan: bad sizes heads=%d per group=%d rows=%d columns=%d", n_heads, heads_per_group, n_rows, n_cols);
   CPI_REQUIRE(n_heads <= 65535, "linear_scan: too many heads (%d)", n_heads);
+  CPI_REQUIRE(decay_kind == 0 || (decay_kind == 1 && z != nullptr && a_log != nullptr),
+              "linear_scan: decay kind %d needs row decays and the heads' rates", decay_kind);
+  CPI_REQUIRE(beta == nullptr || z != nullptr, "linear_scan: the delta rule comes with row decays");
   ScanParams p{k, k_stride, q, q_stride, v, v_stride, z, z_stride, z_bias, inv_tau, dt, dt_stride, dt_bias, a_log,
                skip, small_dtype, q_scale, state, out, out_stride, seq_slot, seq_tok0, seq_new,
-               n_heads, heads_per_group, n_rows, n_cols, 0, 0, decay_ready};
+               n_heads, heads_per_group, n_rows, n_cols, 0, 0, decay_ready, decay_kind, beta, beta_stride};
   if (max_new < 1) max_new = 1;
   return z ? dispatch_scan<true>(p, n_seqs, max_new, stream) : dispatch_scan<false>(p, n_seqs, max_new, stream);
 }
 
 extern "C" int cpi_row_decay(float* z, long z_stride, const void* bias, int bias_dtype, float inv_tau, int n_tokens,
-                             int n, cudaStream_t stream) {
+                             int n, int kind, const void* a_log, int rows_per_head, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   CPI_REQUIRE(n > 0, "row_decay: %d elements a row", n);
-  RowDecayParams p{z, z_stride, bias, bias_dtype, inv_tau, n};
+  CPI_REQUIRE(kind == 0 || (kind == 1 && a_log != nullptr && rows_per_head > 0), "row_decay: kind %d needs the heads' rates", kind);
+  RowDecayParams p{z, z_stride, bias, bias_dtype, inv_tau, n, kind, a_log, rows_per_head};
   cpi::launch_pdl(row_decay_kernel, dim3(n_tokens, (n + 255) / 256), 256, 0, stream, p);
   return check_launch("row_decay");
 }
 
 extern "C" int cpi_gated_norm(const float* y, long y_stride, const float* gate, long gate_stride, const void* w,
                               int w_dtype, int w_len, void* out, int out_dtype, long out_stride, int n_tokens,
-                              int width, int parts, int gate_first, float eps, cudaStream_t stream) {
+                              int width, int parts, int gate_first, float eps, int gate_act, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   CPI_REQUIRE(width > 0 && parts > 0 && width % parts == 0, "gated_norm: %d elements in %d parts", width, parts);
   CPI_REQUIRE(parts <= 65535, "gated_norm: too many parts (%d)", parts);
   CPI_REQUIRE(!w || w_len > 0, "gated_norm: a weight needs a length");
-  GatedNormParams p{y, y_stride, gate, gate_stride, w, w_dtype, w_len, out, out_stride, width, parts, gate_first, eps};
+  CPI_REQUIRE(gate_act == 0 || gate_act == 1, "gated_norm: unknown gate activation %d", gate_act);
+  GatedNormParams p{y, y_stride, gate, gate_stride, w, w_dtype, w_len, out, out_stride, width, parts, gate_first, eps, gate_act};
   CPI_DISPATCH_DTYPE(out_dtype, TO, cpi::launch_pdl(gated_norm_kernel<TO>, dim3(n_tokens, parts), 128, 0, stream, p));
   return check_launch("gated_norm");
+}
+
+extern "C" int cpi_head_unit(float* x, long stride, int n_tokens, int heads, int dim, float eps, cudaStream_t stream) {
+  if (n_tokens == 0 || heads == 0) return 0;
+  CPI_REQUIRE(heads > 0 && dim > 0, "head_unit: %d heads of %d elements", heads, dim);
+  cpi::launch_pdl(head_unit_kernel, dim3(n_tokens, (heads + 3) / 4), 128, 0, stream, x, stride, heads, dim, eps);
+  return check_launch("head_unit");
 }

@@ -64,6 +64,12 @@ class DecoderModel:
         self.logit_softcap = float(spec.head.get("logit_softcap", 0.0) or 0.0)
         self.layer_capture = None           # a list: every run appends the residual after each run entry [T, H]
         self.final_norm = build_part("norm", spec.final_norm, "", workspace=self.ws, tag="norm_final")
+        en = spec.embedding.get("norm")
+        self.embed_norm = None if en is None else build_part("norm", en, "", workspace=self.ws, tag="norm_embed")
+        self.junctions = {name: build_part("junction", js, "", workspace=self.ws) for name, js in spec.junctions}
+        self.keep_x0 = any(j.needs_embedding_output for j in self.junctions.values())
+        if self.embed_norm is not None and self.streams != 1:
+            raise ValueError("a norm on the embedding output does not combine with several residual streams")
         self.embed_name = spec.embedding["weight"]
         self.head_name = spec.head["weight"]
         self.embedding = self.head = None
@@ -73,7 +79,9 @@ class DecoderModel:
     def all_parts(self) -> list:
         """Every part object of the model (layers' blocks, norms, mixers with their position encodings,
         feed-forwards, the final norm)."""
-        out = [self.final_norm]
+        out = [self.final_norm, *self.junctions.values()]
+        if self.embed_norm is not None:
+            out.append(self.embed_norm)
         for layer in self.layers:
             out += layer.all_parts()
         return out
@@ -84,6 +92,10 @@ class DecoderModel:
         if self.head_name != self.embed_name:
             reqs.append(TensorReq(self.head_name, (V, H)))
         reqs += self.final_norm.requirements()
+        if self.embed_norm is not None:
+            reqs += self.embed_norm.requirements()
+        for j in self.junctions.values():
+            reqs += j.requirements()
         for layer in self.layers:
             for p in (layer.block, *layer.parts()):
                 reqs += p.requirements()
@@ -98,6 +110,10 @@ class DecoderModel:
         self.embedding = source.get(self.embed_name, dev).contiguous()
         self.head = self.embedding if self.head_name == self.embed_name else source.get(self.head_name, dev).contiguous()
         self.final_norm.load(source, dev)
+        if self.embed_norm is not None:
+            self.embed_norm.load(source, dev)
+        for j in self.junctions.values():
+            j.load(source, dev)
         for layer in self.layers:
             for p in (layer.block, *layer.parts()):
                 p.load(source, dev)
@@ -129,11 +145,23 @@ class DecoderModel:
         xs = self.ws.get("residual", (S, T, H), torch.float32)
         self.ws.pending_writeback = None
         with phase("embedding"):
-            for s in range(S):
-                K.embedding(batch.tokens, self.embedding, xs[s], self.err_flag)
+            if self.embed_norm is not None:                 # the looked-up rows are normed into the residual
+                raw = self.ws.get("embed_rows", (T, H), torch.float32)
+                K.embedding(batch.tokens, self.embedding, raw, self.err_flag)
+                self.embed_norm(raw, torch.float32, out=xs[0])
+            else:
+                for s in range(S):
+                    K.embedding(batch.tokens, self.embedding, xs[s], self.err_flag)
         x = xs[0] if S == 1 else xs
+        x0 = None
+        if self.keep_x0:
+            x0 = self.ws.get("embed_out", (T, H), torch.float32)
+            x0.copy_(xs[0])
         for i, e in enumerate(self.spec.run_order):
             layer = self.layers[e.layer]
+            if e.before is not None:
+                self.ws.settle()                # a block may have left its last write-back to whoever reads x next
+                self.junctions[e.before].run(x, x0, batch)
             owner = i if e.cache_of is None else e.cache_of
             view = parts_base.CacheView(cache_manager, owner, owns=e.cache_of is None)
             layer.block.run(layer, x, batch, view)

@@ -18,7 +18,9 @@ weights, before the rotation; "head" is the weightless per-head norm above), sin
 exponential joins the softmax denominator without a key or a value), a position part that rotates only the first
 elements of a head, and tensor_names {"q", "k", "v", "o", "q_bias", "k_bias", "v_bias", "q_norm", "k_norm", "sink"}.
 A mixer that uses one of them prepares q, k and v with the general kernel (`qkv_prepare`), from float32 projection
-rows, so that a row is rounded once, after its norm and rotation.
+rows, so that a row is rounded once, after its norm and rotation.  There the weightless per-head norm comes after
+the rotation (qk_norm_order "after_rope").  A sliding window may carry `keep_first`: the sequence's first positions
+stay visible to every later query, at their own positions.
 """
 from __future__ import annotations
 
@@ -74,11 +76,15 @@ class AttentionMixer(Mixer):
         self.w_qkv = self.w_o = None
         self.rotary = self.score_bias = None
         self.b_qkv = self.w_qnorm = self.w_knorm = self.sink = None
-        if self.general and (self.temperature is not None or (self.qk_norm and self.norm_scope == "head")
-                             or not self.norm_before_rope and self.qk_norm):
+        self.keep_first = int(w.get("keep_first") or 0) if self.window_kind == "sliding" else 0
+        if self.keep_first < 0:
+            raise ValueError(f"attention: keep_first must not be negative, not {self.keep_first}")
+        head_norm = self.qk_norm and self.norm_scope == "head"
+        if self.general and (self.temperature is not None or (head_norm and self.norm_before_rope)
+                             or (self.qk_norm and not head_norm and not self.norm_before_rope)):
             raise ValueError("attention: biases, a norm over the whole projection, a partial rotation or values of "
-                             "another size do not combine with the per-head norm, a norm after the rotation or the "
-                             "query temperature")
+                             "another size do not combine with a per-head norm before the rotation, a whole-projection "
+                             "norm after it, or the query temperature")
         a = "self_attn."
         self.tn = {"q": a + "q_proj.weight", "k": a + "k_proj.weight", "v": a + "v_proj.weight",
                    "o": a + "o_proj.weight", "q_bias": a + "q_proj.bias", "k_bias": a + "k_proj.bias",
@@ -144,8 +150,8 @@ class AttentionMixer(Mixer):
     def kv_requirement(self):
         if self.dv != self.d:
             return KVRequirement(self.nkv, self.d, self.window_kind, self.window_size,
-                                 streams=(("k", self.nkv, self.d), ("v", self.nkv, self.dv)))
-        return KVRequirement(self.nkv, self.d, self.window_kind, self.window_size)
+                                 streams=(("k", self.nkv, self.d), ("v", self.nkv, self.dv)), keep_first=self.keep_first)
+        return KVRequirement(self.nkv, self.d, self.window_kind, self.window_size, keep_first=self.keep_first)
 
     # ---- step ------------------------------------------------------------------------------------
     can_store = True          # forward(..., add=False) stores the mixer's output (float32) instead of adding it
@@ -166,7 +172,8 @@ class AttentionMixer(Mixer):
                 K.qkv_prepare(qkv, q, k_cache, v_cache, table, page_size, batch.token_seq, batch.token_pos,
                               batch.seq_slot, n_heads=self.nh, n_kv_heads=self.nkv, head_dim=self.d,
                               value_dim=self.dv, bias=self.b_qkv, q_norm=self.w_qnorm, k_norm=self.w_knorm,
-                              norm_whole=self.qk_norm, norm_eps=self.qk_norm_eps,
+                              norm_whole=self.qk_norm and self.norm_scope == "projection",
+                              head_norm=self.qk_norm and self.norm_scope == "head", norm_eps=self.qk_norm_eps,
                               inv_freq=None if self.rotary is None else self.rotary.inv_freq,
                               rotary_dims=self.rot_dims if self.rotary is not None else 0,
                               write_kv=self.has_kv and cache.owns)
@@ -190,8 +197,10 @@ class AttentionMixer(Mixer):
 
     def attend(self, q, att, k_cache, v_cache, table, page_size, batch):
         wk = K.WINDOW_KINDS[self.window_kind]
-        # the tensor-core kernels add nothing to a score and take keys and values of one size
-        tensor_cores = use_tensor_core_kernels and self.score_bias is None and self.dv == self.d
+        # the tensor-core kernels add nothing to a score, take keys and values of one size and a window without
+        # kept first positions
+        tensor_cores = (use_tensor_core_kernels and self.score_bias is None and self.dv == self.d
+                        and self.keep_first == 0)
         if (tensor_cores and batch.is_decode and q.dtype == torch.bfloat16
                 and K.attention_decode_supported(self.nh, self.nkv, self.d, page_size)):
             # keys per sequence that the window lets through, at most (a bucketed bound: the split count
@@ -222,4 +231,5 @@ class AttentionMixer(Mixer):
         K.attention_general(q, att, k_cache, v_cache, table, page_size, batch.token_seq, batch.token_pos,
                             batch.seq_slot, n_heads=self.nh, n_kv_heads=self.nkv, head_dim=self.d,
                             window_kind=K.WINDOW_KINDS[self.window_kind], window_size=self.window_size,
-                            scale=self.scale, score_bias=self.score_bias, sink=self.sink, value_dim=self.dv)
+                            scale=self.scale, score_bias=self.score_bias, sink=self.sink, value_dim=self.dv,
+                            keep_first=self.keep_first)

@@ -13,6 +13,8 @@ Mixer         requirements(); load(src, dev); kv_requirement(); state_requiremen
               forward(h, residual, batch, cache)        # residual += mixer(h)
 FeedForward   requirements(); load(src, dev); forward(h, residual, batch)   # residual += ffn(h)
 Block         run(layer, residual, batch, cache)        # the arrangement of the above
+Junction      requirements(); load(src, dev); run(x, x0, batch)   # between two layers: rewrites the residual x in
+              place; x0 is the embedding output (kept by the model when a junction sets `needs_embedding_output`)
 
 `h` is the normed input in the activation dtype [tokens, hidden]; `residual` is the float32 residual
 stream [tokens, hidden], updated in place.  A mixer must give the same result for a position whether
@@ -105,6 +107,13 @@ class Block(Part):
         raise NotImplementedError
 
 
+class Junction(Part):
+    needs_embedding_output = False
+
+    def run(self, x, x0, batch) -> None:
+        raise NotImplementedError
+
+
 class CacheView:
     """What a mixer sees of the cache during one step, for its run entry."""
 
@@ -126,7 +135,7 @@ class CacheView:
         return self._m.state_view(self._entry, name)
 
 
-_REGISTRIES: dict = {"norm": {}, "position": {}, "mixer": {}, "feed_forward": {}, "block": {}}
+_REGISTRIES: dict = {"norm": {}, "position": {}, "mixer": {}, "feed_forward": {}, "block": {}, "junction": {}}
 
 
 def _register(family: str, kind: str) -> Callable:
@@ -141,6 +150,7 @@ def register_position(kind): return _register("position", kind)
 def register_mixer(kind): return _register("mixer", kind)
 def register_feed_forward(kind): return _register("feed_forward", kind)
 def register_block(kind): return _register("block", kind)
+def register_junction(kind): return _register("junction", kind)
 
 
 def build_part(family: str, spec: PartSpec, prefix: str = "", **kw):

@@ -11,6 +11,10 @@ sublayer before and forms and normalises the next u; the write-back of a layer's
 the workspace and done by the next layer's first kernel (or by `Workspace.settle()` when something else reads the
 residual first), so a layer costs as many of these launches as it has sublayers.  A layer without a feed-forward
 has the first sublayer only.
+
+"scaled_pre_norm": x += m * mixer(norm1(x)); x += m * ffn(norm2(x)) with one constant m (`residual_scale`).  It is the
+arrangement above with a single stream and constant coefficients (read 1, mix 1, write m), so the scaled addition of a
+sublayer's output rides on the kernel that forms the next sublayer's normed input.
 """
 from __future__ import annotations
 
@@ -117,3 +121,23 @@ class HyperConnectionsBlock(Block):
             self._run_part(layer.feed_forward, h2, y2, batch)
             pending = (y2, self.coef[1])
         ws.pending_writeback = (x, pending[0], pending[1][1], pending[1][2])
+
+
+@register_block("scaled_pre_norm")
+class ScaledPreNormBlock(HyperConnectionsBlock):
+    """params: residual_scale (m).  No tensors of its own."""
+    graph_safe = True
+
+    def __init__(self, spec, prefix="", **_):
+        Block.__init__(self, spec, prefix)
+        self.S, self.names, self.required = 1, [], False
+        self.scale = float(spec["residual_scale"])
+        self.coef = []
+
+    def requirements(self):
+        return []
+
+    def load(self, source, device):
+        one = torch.ones(1, dtype=torch.float32, device=device)
+        c = (one, torch.full((1,), self.scale, dtype=torch.float32, device=device), one.view(1, 1).clone())
+        self.coef = [c, c]

@@ -6,10 +6,17 @@ expert with ordinary [out, in] matrices, both added to the residual.  The refere
 and no gate value; top-k and the sigmoid gate (on the expert's input or output) are parameters here.
 
 dense_swiglu  params: hidden_size, intermediate_size, activation ("silu" by default, or "gelu_tanh": the gate's
-              activation; down(act(gate h) * (up h))), tensor_names (gate, up, down under the prefix)
+              activation; down(act(gate h) * (up h)); or "swish_clamped" with `limit`: g = min(gate h, limit),
+              u = clamp(up h, -limit, limit), down(g sigmoid(1.702 g) (u + 1))), tensor_names (gate, up, down under
+              the prefix), token_gate (a tensor name [1, H] or None: the output of a token is multiplied by
+              sigmoid(token_gate . h))
               tensors: feed_forward.{gate,up,down}_proj.weight
 moe_swiglu    params: hidden_size, num_experts, top_k, expert_size, shared_size (0 = no shared expert),
-              router_gate ("sigmoid_input" | "sigmoid_output" | "none")
+              router_gate ("sigmoid_input" | "sigmoid_output" | "none" | "softmax_chosen": the chosen experts'
+              outputs weighted by the softmax over their logits), router_bias (a tensor name [E] added to the logits,
+              or None), expert_layout ("stacked", below, or "per_expert": `expert_names` {"gate", "up", "down"} with
+              "{e}" for the expert's number, each [out, in]), router_name, shared (None or the params of a
+              dense_swiglu part that runs for every token beside the routed experts, instead of shared_size)
               tensors: feed_forward.router.weight [E, H], feed_forward.experts.gate_up_proj [E, H, 2I],
               feed_forward.experts.down_proj [E, I, H], feed_forward.shared_expert.{gate,up,down}_proj.weight
 
@@ -50,31 +57,52 @@ class DenseSwiGLU(FeedForward):
         self.activation = spec.get("activation", "silu")
         if self.activation not in K.GATE_ACTS:
             raise ValueError(f"dense_swiglu: unknown activation '{self.activation}'; known: {sorted(K.GATE_ACTS)}")
+        self.limit = float(spec.get("limit") or 0.0)
+        if self.activation == "swish_clamped" and not self.limit > 0:
+            raise ValueError("dense_swiglu: the clamped activation needs a positive limit")
         tn = spec.get("tensor_names")
         if tn:
             names = (tn["gate"], tn["up"], tn["down"])
         self.names = tuple(prefix + n for n in names)
+        self.token_gate_name = None if spec.get("token_gate") is None else prefix + spec["token_gate"]
         self.ws = workspace
-        self.w_gate_up = self.w_down = None
+        self.w_gate_up = self.w_down = self.w_token_gate = None
 
     def requirements(self):
         g, u, d = self.names
-        return [TensorReq(g, (self.inter, self.hidden)), TensorReq(u, (self.inter, self.hidden)),
+        reqs = [TensorReq(g, (self.inter, self.hidden)), TensorReq(u, (self.inter, self.hidden)),
                 TensorReq(d, (self.hidden, self.inter))]
+        if self.token_gate_name is not None:
+            reqs.append(TensorReq(self.token_gate_name, (1, self.hidden)))
+        return reqs
 
     def load(self, source, device):
         g, u, d = self.names
         self.w_gate_up = _stack(source.get(g, device), source.get(u, device))
         self.w_down = source.get(d, device).contiguous()
+        if self.token_gate_name is not None:
+            self.w_token_gate = source.get(self.token_gate_name, device).contiguous()
 
     can_store = True          # forward(..., add=False) stores the output (float32) instead of adding it
 
     def forward(self, h, residual, batch, add=True):
-        a = self.ws.get("ffn_act", (h.shape[0], self.inter), h.dtype)
+        T = h.shape[0]
+        a = self.ws.get("ffn_act", (T, self.inter), h.dtype)
         with phase("mlp"):
-            # the gate's activation and the product with `up` happen in the epilogue of the first product
-            project(h, self.w_gate_up, a, MODE_SWIGLU if self.activation == "silu" else MODE_GEGLU)
-            project(a, self.w_down, residual, MODE_ADD if add else MODE_STORE)
+            scale = None
+            if self.w_token_gate is not None:
+                # one number per token, sigmoid(w . h) in float32: the router's kernels with a single expert
+                scale = self.ws.get("ffn_token_gate", (T, 1), torch.float32)
+                K.router_topk(h, self.w_token_gate, self.ws.get("ffn_token_gate_idx", (T, 1), torch.int32), scale,
+                              top_k=1, sigmoid_gate=True, logits_out=self.ws.get("ffn_token_gate_z", (T, 1), torch.float32))
+            if self.activation == "swish_clamped":
+                gu = self.ws.get("ffn_gate_up", (T, 2 * self.inter), torch.float32)
+                project(h, self.w_gate_up, gu)
+                K.gated_act(gu, a, self.activation, self.limit)
+            else:
+                # the gate's activation and the product with `up` happen in the epilogue of the first product
+                project(h, self.w_gate_up, a, MODE_SWIGLU if self.activation == "silu" else MODE_GEGLU)
+            project(a, self.w_down, residual, MODE_ADD if add else MODE_STORE, row_scale=scale)
 
 
 @register_feed_forward("moe_swiglu")
@@ -86,7 +114,7 @@ class MoESwiGLU(FeedForward):
         self.hidden, self.n_experts, self.top_k = int(p["hidden_size"]), int(p["num_experts"]), int(p["top_k"])
         self.inter, self.shared_inter = int(p["expert_size"]), int(p.get("shared_size", 0))
         self.gate_mode = p.get("router_gate", "sigmoid_input")
-        if self.gate_mode not in ("sigmoid_input", "sigmoid_output", "none"):
+        if self.gate_mode not in ("sigmoid_input", "sigmoid_output", "none", "softmax_chosen"):
             raise ValueError(f"moe_swiglu: unknown router_gate '{self.gate_mode}'")
         if not 1 <= self.top_k <= self.n_experts:
             raise ValueError(f"moe_swiglu: top_k {self.top_k} of {self.n_experts} experts")
@@ -95,8 +123,22 @@ class MoESwiGLU(FeedForward):
         self.ws = workspace
         f = prefix + "feed_forward."
         self.n_router, self.n_gate_up, self.n_down = f + "router.weight", f + "experts.gate_up_proj", f + "experts.down_proj"
+        if p.get("router_name"):
+            self.n_router = prefix + p["router_name"]
+        self.n_router_bias = None if p.get("router_bias") is None else prefix + p["router_bias"]
+        self.layout = p.get("expert_layout", "stacked")
+        if self.layout not in ("stacked", "per_expert"):
+            raise ValueError(f"moe_swiglu: unknown expert_layout '{self.layout}'")
+        self.expert_names = {k: prefix + v for k, v in (p.get("expert_names") or {}).items()}
+        if self.layout == "per_expert" and set(self.expert_names) != {"gate", "up", "down"}:
+            raise ValueError("moe_swiglu: the per_expert layout needs expert_names for gate, up and down")
+        self.b_router = None
         self.shared = None
-        if self.shared_inter > 0:
+        if p.get("shared") is not None:
+            from ..config.spec import PartSpec
+            self.shared = DenseSwiGLU(PartSpec("dense_swiglu", {"hidden_size": self.hidden, **p["shared"]}), prefix, workspace)
+            self.shared_inter = self.shared.inter
+        elif self.shared_inter > 0:
             from ..config.spec import PartSpec
             self.shared = DenseSwiGLU(
                 PartSpec("dense_swiglu", {"hidden_size": self.hidden, "intermediate_size": self.shared_inter}),
@@ -115,17 +157,34 @@ class MoESwiGLU(FeedForward):
         self.capture = None        # a list: every forward appends a copy of its expert choices [T, k]
 
     def requirements(self):
-        reqs = [TensorReq(self.n_router, (self.n_experts, self.hidden)),
-                TensorReq(self.n_gate_up, (self.n_experts, self.hidden, 2 * self.inter)),
-                TensorReq(self.n_down, (self.n_experts, self.inter, self.hidden))]
+        reqs = [TensorReq(self.n_router, (self.n_experts, self.hidden))]
+        if self.n_router_bias is not None:
+            reqs.append(TensorReq(self.n_router_bias, (self.n_experts,)))
+        if self.layout == "per_expert":
+            for e in range(self.n_experts):
+                reqs += [TensorReq(self.expert_names["gate"].format(e=e), (self.inter, self.hidden)),
+                         TensorReq(self.expert_names["up"].format(e=e), (self.inter, self.hidden)),
+                         TensorReq(self.expert_names["down"].format(e=e), (self.hidden, self.inter))]
+        else:
+            reqs += [TensorReq(self.n_gate_up, (self.n_experts, self.hidden, 2 * self.inter)),
+                     TensorReq(self.n_down, (self.n_experts, self.inter, self.hidden))]
         if self.shared is not None:
             reqs += self.shared.requirements()
         return reqs
 
     def load(self, source, device):
         self.w_router = source.get(self.n_router, device).contiguous()
-        self.w_gate_up = _turned(source.get(self.n_gate_up, device))          # [E, 2I, H]
-        self.w_down = _turned(source.get(self.n_down, device))                # [E, H, I]
+        if self.n_router_bias is not None:
+            self.b_router = source.get(self.n_router_bias, device).to(torch.float32).contiguous()
+        if self.layout == "per_expert":                                       # stored [out, in] already
+            n = self.expert_names
+            self.w_gate_up = torch.stack([_stack(source.get(n["gate"].format(e=e), device), source.get(n["up"].format(e=e), device))
+                                          for e in range(self.n_experts)]).contiguous()             # [E, 2I, H]
+            self.w_down = torch.stack([source.get(n["down"].format(e=e), device)
+                                       for e in range(self.n_experts)]).contiguous()                # [E, H, I]
+        else:
+            self.w_gate_up = _turned(source.get(self.n_gate_up, device))          # [E, 2I, H]
+            self.w_down = _turned(source.get(self.n_down, device))                # [E, H, I]
         if self.shared is not None:
             self.shared.load(source, device)
 
@@ -156,7 +215,8 @@ class MoESwiGLU(FeedForward):
         sorted_h = ws.get("moe_in", (M, self.hidden), h.dtype) if sortable else None
         with phase("moe_router"):
             gathered = K.moe_route(h, self.w_router, idx, gate, logits, offsets, row_token, row_scale, row_of_slot,
-                                   top_k=Kk, sigmoid_gate=self.gate_mode != "none", sorted_h=sorted_h)
+                                   top_k=Kk, sorted_h=sorted_h, bias=self.b_router,
+                                   sigmoid_gate="softmax_chosen" if self.gate_mode == "softmax_chosen" else self.gate_mode != "none")
         if self.capture is not None:
             self.capture.append(idx.clone())
         hint = max(1, -(-M // E))
@@ -171,7 +231,7 @@ class MoESwiGLU(FeedForward):
             else:
                 project(h, self.w_gate_up, act, MODE_SWIGLU, m_rows=M, a_rows=row_token, row_scale=in_scale,
                         group_offsets=offsets, n_groups=E, rows_per_group_hint=hint)
-            out_scale = row_scale if self.gate_mode == "sigmoid_output" else None
+            out_scale = row_scale if self.gate_mode in ("sigmoid_output", "softmax_chosen") else None
             # One expert per token: the down projection can add straight into the residual rows.  Beside a shared
             # expert on the second stream that needs an order (two kernels adding into the same rows at once would
             # sum in whatever order they meet): in a step with many tokens the join comes before the down

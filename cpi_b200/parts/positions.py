@@ -37,13 +37,19 @@ def llama3_frequencies(head_dim: int, theta: float, scaling) -> np.ndarray:
 @register_position("rope")
 class RotaryPosition(Position):
     """params: head_dim, theta, pairing ("half_split" pairs (d, d+D/2); "interleaved" pairs (2d, 2d+1)),
-    scaling (None or the llama3 dictionary), rotary_dims (None: the whole head; n: only the first n elements of a
-    head turn, as pairs (d, d + n/2) with frequencies theta^(-2d/n), the rest pass unchanged)."""
+    scaling (None, the llama3 dictionary, or {"rope_type": "linear", "factor": f}: every frequency divided by f), rotary_dims (None: the whole head; n: only the first n elements of a
+    head turn, as pairs (d, d + n/2) with frequencies theta^(-2d/n), the rest pass unchanged), frequency_math
+    ("float32": the powers as the reference computes them; "float64": in double precision, rounded once)."""
     graph_safe = True
 
     def __init__(self, spec, prefix=""):
         super().__init__(spec, prefix)
         sc = spec.get("scaling")
+        linear = None
+        if sc is not None and sc.get("rope_type", "llama3") == "linear":
+            linear, sc = float(sc["factor"]), None         # every frequency divided by one factor
+            if not linear > 0:
+                raise ValueError(f"rope: a linear scaling factor must be positive, not {linear}")
         if sc is not None and sc.get("rope_type", "llama3") != "llama3":
             raise ValueError(f"rope scaling of type '{sc.get('rope_type')}' is not supported")
         if spec["pairing"] not in ("half_split", "interleaved"):
@@ -53,7 +59,14 @@ class RotaryPosition(Position):
         dims = int(spec["head_dim"]) if dims is None else int(dims)
         if dims < 2 or dims % 2 or dims > int(spec["head_dim"]):
             raise ValueError(f"rope: {dims} rotated elements of a head of {spec['head_dim']}")
-        self.frequencies = llama3_frequencies(dims, float(spec["theta"]), sc)
+        if spec.get("frequency_math", "float32") == "float64" and sc is None:
+            # theta^(-2d/n) / factor in double precision, rounded once
+            f = np.float64(spec["theta"]) ** (-2.0 * np.arange(dims // 2, dtype=np.float64) / dims)
+            self.frequencies = (f / (linear or 1.0)).astype(np.float32)
+        else:
+            self.frequencies = llama3_frequencies(dims, float(spec["theta"]), sc)
+            if linear is not None:
+                self.frequencies = (self.frequencies.astype(np.float64) / linear).astype(np.float32)
         self.inv_freq = None
 
     def prepare(self, device):

@@ -180,3 +180,102 @@ class GLAMixer(Mixer):
             K.gated_norm(o, proj[:, 2 * nk + nv:], self.w_norm, g, parts=self.nh, gate_first=False, eps=self.eps)
         with phase("wo"):
             project(g, self.w_o, residual, MODE_ADD if add else MODE_STORE)
+
+
+@register_mixer("gated_delta")
+class GatedDeltaMixer(Mixer):
+    """The gated delta rule: a matrix state per head that forgets per key channel and is corrected, not just added to.
+
+        q = W_q h, k = W_k h (kv_heads heads of key_dim), v = W_v h (heads of value_dim); each passes a short causal
+        convolution per channel (no bias) and silu; q and k become unit vectors per head, x / sqrt(sum x^2 + unit_eps);
+        beta = sigmoid(W_b h) per head;  a = exp(-exp(A_log[head]) softplus(W_a2 (W_a1 h) + dt_bias)) per head and key channel;
+        S <- diag(a) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q / sqrt(key_dim)   (head h reads q/k head h // (heads / kv_heads));
+        out = W_o concat_heads(rmsnorm(o_head) * norm * sigmoid(W_g2 (W_g1 h)))   -- norm weight shared by the heads.
+
+    params: hidden_size, heads, kv_heads, key_dim, value_dim, conv (taps), decay_rank, gate_rank, norm_eps, unit_eps,
+    tensor_names {"q", "k", "v", "q_conv", "k_conv", "v_conv", "b", "A_log", "dt_bias", "a1", "a2", "g1", "g2", "norm", "o"}.
+    state: "s" [heads, key_dim, value_dim] float32, "conv" [conv - 1, channels] (the last inputs of the convolutions).
+    Decays, beta, the unit vectors and the state are float32 in both precisions."""
+    graph_safe = True
+    can_store = True
+
+    def __init__(self, spec, prefix="", workspace=None, owns_cache=True):
+        super().__init__(spec, prefix)
+        p = spec.params
+        self.hidden, self.nh, self.nkv = int(p["hidden_size"]), int(p["heads"]), int(p.get("kv_heads") or p["heads"])
+        self.dk, self.dv, self.taps = int(p["key_dim"]), int(p["value_dim"]), int(p.get("conv") or 1)
+        self.rank_a, self.rank_g = int(p["decay_rank"]), int(p["gate_rank"])
+        self.eps, self.unit_eps = float(p["norm_eps"]), float(p.get("unit_eps", 1e-6))
+        if self.nh % self.nkv:
+            raise ValueError(f"gated_delta: {self.nh} heads cannot share {self.nkv} heads of q and k")
+        if not 1 <= self.taps <= 8:
+            raise ValueError(f"gated_delta: a convolution of {self.taps} taps (supported: 1 to 8)")
+        if not owns_cache:
+            raise ValueError("gated_delta: a recurrent layer cannot read another run entry's state")
+        self.nqk, self.nv = self.nkv * self.dk, self.nh * self.dv
+        self.channels = 2 * self.nqk + self.nv                       # what the convolutions run over: q | k | v
+        tn = {"q": "mixer.q_proj.weight", "k": "mixer.k_proj.weight", "v": "mixer.v_proj.weight",
+              "q_conv": "mixer.q_conv.weight", "k_conv": "mixer.k_conv.weight", "v_conv": "mixer.v_conv.weight",
+              "b": "mixer.b_proj.weight", "A_log": "mixer.A_log", "dt_bias": "mixer.dt_bias",
+              "a1": "mixer.a_proj.0.weight", "a2": "mixer.a_proj.1.weight", "g1": "mixer.g_proj.0.weight",
+              "g2": "mixer.g_proj.1.weight", "norm": "mixer.o_norm.weight", "o": "mixer.o_proj.weight"}
+        tn.update(p.get("tensor_names") or {})
+        self.tn = {k: prefix + v for k, v in tn.items()}
+        self.ws = workspace
+        self.w_in = self.w_conv = self.w_a2 = self.w_g2 = self.dt_bias = self.a_log = self.w_norm = self.w_o = None
+
+    def requirements(self):
+        t, H = self.tn, self.hidden
+        return [TensorReq(t["q"], (self.nqk, H)), TensorReq(t["k"], (self.nqk, H)), TensorReq(t["v"], (self.nv, H)),
+                TensorReq(t["q_conv"], (self.nqk, self.taps), init="const:0.3+normal"),
+                TensorReq(t["k_conv"], (self.nqk, self.taps), init="const:0.3+normal"),
+                TensorReq(t["v_conv"], (self.nv, self.taps), init="const:0.3+normal"),
+                TensorReq(t["b"], (self.nh, H)), TensorReq(t["A_log"], (self.nh,)),
+                TensorReq(t["dt_bias"], (self.nh * self.dk,)),
+                TensorReq(t["a1"], (self.rank_a, H)), TensorReq(t["a2"], (self.nh * self.dk, self.rank_a)),
+                TensorReq(t["g1"], (self.rank_g, H)), TensorReq(t["g2"], (self.nv, self.rank_g)),
+                TensorReq(t["norm"], (self.dv,), init="ones+normal"), TensorReq(t["o"], (H, self.nv))]
+
+    def load(self, source, device):
+        t = self.tn
+        f32 = lambda name: source.get(t[name], device).to(torch.float32).contiguous()
+        self.w_in = _cat_rows([source.get(t[n], device) for n in ("q", "k", "v", "b", "a1", "g1")])
+        self.w_conv = torch.cat([f32("q_conv"), f32("k_conv"), f32("v_conv")], dim=0).contiguous()
+        self.w_a2 = source.get(t["a2"], device).contiguous()
+        self.w_g2 = source.get(t["g2"], device).contiguous()
+        self.dt_bias, self.a_log, self.w_norm = f32("dt_bias"), f32("A_log"), f32("norm")
+        self.w_o = source.get(t["o"], device).contiguous()
+
+    def state_requirements(self):
+        return [StateRequirement("s", (self.nh, self.dk, self.dv)),
+                StateRequirement("conv", (max(self.taps - 1, 0), self.channels))]
+
+    def forward(self, h, residual, batch, cache, add=True):
+        T, f32 = h.shape[0], torch.float32
+        C, nqk, nv = self.channels, self.nqk, self.nv
+        o_b, o_a, o_g = C, C + self.nh, C + self.nh + self.rank_a
+        proj = self.ws.get("gdr_proj", (T, o_g + self.rank_g), f32)
+        z = self.ws.get("gdr_z", (T, self.nh * self.dk), f32)
+        gate = self.ws.get("gdr_gate", (T, nv), f32)
+        with phase("qkv"):
+            project(h, self.w_in, proj)
+            project(proj[:, o_a:o_g], self.w_a2, z)
+            project(proj[:, o_g:], self.w_g2, gate)
+        qkv = self.ws.get("gdr_qkv", (T, C), f32)
+        with phase("conv"):
+            K.causal_conv(proj[:, :C], self.w_conv, None, cache.state("conv"), qkv, batch, silu=True)
+            K.head_unit(qkv[:, :2 * nqk], heads=2 * self.nkv, dim=self.dk, eps=self.unit_eps)
+        o = self.ws.get("gdr_o", (T, nv), f32)
+        with phase("scan"):
+            ready = batch.max_new > DECAY_PREPASS_FROM
+            if ready:
+                K.row_decay(z, self.dt_bias, 1.0, kind=1, a_log=self.a_log, rows_per_head=self.dk)
+            K.linear_scan(qkv[:, nqk:2 * nqk], qkv[:, :nqk], qkv[:, 2 * nqk:], cache.state("s"), o, batch,
+                          n_heads=self.nh, heads_per_group=self.nh // self.nkv, n_rows=self.dk, n_cols=self.dv, z=z,
+                          z_bias=self.dt_bias, a_log=self.a_log, decay_kind=1, decay_ready=ready,
+                          q_scale=self.dk ** -0.5, beta=proj[:, o_b:o_a])
+        with phase("gated_norm"):
+            g = self.ws.get("gdr_gated", (T, nv), h.dtype)
+            K.gated_norm(o, gate, self.w_norm, g, parts=self.nh, gate_first=False, eps=self.eps, gate_act="sigmoid")
+        with phase("wo"):
+            project(g, self.w_o, residual, MODE_ADD if add else MODE_STORE)
