@@ -199,7 +199,7 @@ def run_order(cfg):
 def forward(cfg, weights, tokens, layers_out=None):
     """Logits [T, vocab] of one whole sequence; `layers_out` (a list) receives the residual after every layer run."""
     w = {k: v.to(F64) for k, v in weights.items()}
-    eps, mult = cfg["norm"]["eps"], cfg["residual_mult"]
+    eps, mult = cfg["norm"]["eps"], cfg.get("residual_mult", 1.0)
     T = len(tokens)
     positions = torch.arange(T)
     x = rms_norm(w["embed"][torch.tensor(tokens)], w["embed.norm"], eps)
