@@ -37,6 +37,9 @@ its wall-clock phases, second of two runs.
 state-space layer; gelu-gated feed-forwards; two residual streams) at two layer sizes, six layers each, beside the
 dense Llama4-style decoder at the same sizes: one prefill of 2,048 tokens and decode at batch 8, device-timed, then
 the time of every phase and each phase's fraction of its roofline for both models.
+`--workload savenex`: the Savenex design (windowed attention with kept first tokens beside a gated delta rule in every
+layer, dense and routed feed-forwards, a looped range) at two layer sizes beside Veredra's attention and
+gated-linear-attention layers at the same sizes, measured the same way.
 """
 from __future__ import annotations
 
@@ -633,6 +636,61 @@ def llama_dense_config(sz: dict, vocab: int, layers: int) -> dict:
     return cfg
 
 
+def measure_config(cfg, vocab, T, B, toks):
+    """One model drawn from `cfg`: a prompt of T tokens (median of five after a warm-up), decode at batch B on a
+    context of T - 64 (32 steps, device-timed), then the phases of one prompt and of four decode steps (eager, one
+    stream)."""
+    import torch
+    from cpi_b200.engine import Engine, StepEntry
+    eng = Engine.from_random(cfg, 0, dtype="bfloat16", max_tokens=(B + 1) * (T + 128), max_seqs=B + 1,
+                             max_seq_len=T + 128)
+    res = {}
+
+    def prefill():
+        s = eng.acquire_slot()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        eng.step([StepEntry(s, toks(T), [T - 1])])
+        e1.record()
+        torch.cuda.synchronize()
+        eng.release_slot(s)
+        return e0.elapsed_time(e1)
+
+    times = sorted(prefill() for _ in range(6))[:-1]          # the first (slowest) pass warms up
+    res["prefill_ms"] = round(times[len(times) // 2], 3)
+    res["prefill_tok_s"] = round(T / (res["prefill_ms"] / 1e3), 1)
+    slots = [eng.acquire_slot() for _ in range(B)]
+    eng.step([StepEntry(s, toks(T - 64), []) for s in slots])
+    for _ in range(8):
+        eng.step([StepEntry(s, toks(1), [0]) for s in slots])
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(32):
+        eng.step([StepEntry(s, toks(1), [0]) for s in slots])
+    e1.record()
+    torch.cuda.synchronize()
+    res["decode_ms_per_step"] = round(e0.elapsed_time(e1) / 32, 4)
+    res["decode_tok_s"] = round(B / (res["decode_ms_per_step"] / 1e3), 1)
+    res["graphs"] = bool(eng.use_graphs)
+    timer = eng.profile_phases(True)
+    for _ in range(4):
+        eng.step([StepEntry(s, toks(1), [0]) for s in slots])
+    for s in slots:
+        eng.release_slot(s)
+    s = eng.acquire_slot()
+    eng.step([StepEntry(s, toks(T), [T - 1])])
+    eng.release_slot(s)
+    ph = timer.collect()
+    eng.profile_phases(False)
+    res["phases_ms"] = {"prefill": {k: round(v, 4) for k, v in ph.get("prefill", {}).items()},
+                        "decode_per_step": {k: round(v / 4, 4) for k, v in ph.get("decode", {}).items()}}
+    del eng
+    torch.cuda.empty_cache()
+    return res
+
+
+
 def run_veredra(args) -> dict:
     """Prefill and decode of Veredra at two layer sizes beside the dense Llama4-style decoder at equal sizes, with
     the time of every phase per layer that has it and each phase's share of its roofline (products: flops over the
@@ -648,53 +706,7 @@ def run_veredra(args) -> dict:
     out = {"metric": "tokens/s, Veredra beside the dense decoder at equal layer sizes (bf16, random weights)",
            "unit": "tokens/s", "dtype": "bf16", "data": "synthetic", "peaks": pk, "points": {}}
 
-    def measure(cfg, n_layers):
-        eng = Engine.from_random(cfg, 0, dtype="bfloat16", max_tokens=(B + 1) * (T + 128), max_seqs=B + 1,
-                                 max_seq_len=T + 128)
-        res = {}
-
-        def prefill():
-            s = eng.acquire_slot()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            eng.step([StepEntry(s, toks(T), [T - 1])])
-            e1.record()
-            torch.cuda.synchronize()
-            eng.release_slot(s)
-            return e0.elapsed_time(e1)
-
-        times = sorted(prefill() for _ in range(6))[:-1]          # the first (slowest) pass warms up
-        res["prefill_ms"] = round(times[len(times) // 2], 3)
-        res["prefill_tok_s"] = round(T / (res["prefill_ms"] / 1e3), 1)
-        slots = [eng.acquire_slot() for _ in range(B)]
-        eng.step([StepEntry(s, toks(T - 64), []) for s in slots])
-        for _ in range(8):
-            eng.step([StepEntry(s, toks(1), [0]) for s in slots])
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(32):
-            eng.step([StepEntry(s, toks(1), [0]) for s in slots])
-        e1.record()
-        torch.cuda.synchronize()
-        res["decode_ms_per_step"] = round(e0.elapsed_time(e1) / 32, 4)
-        res["decode_tok_s"] = round(B / (res["decode_ms_per_step"] / 1e3), 1)
-        res["graphs"] = bool(eng.use_graphs)
-        timer = eng.profile_phases(True)
-        for _ in range(4):
-            eng.step([StepEntry(s, toks(1), [0]) for s in slots])
-        for s in slots:
-            eng.release_slot(s)
-        s = eng.acquire_slot()
-        eng.step([StepEntry(s, toks(T), [T - 1])])
-        eng.release_slot(s)
-        ph = timer.collect()
-        eng.profile_phases(False)
-        res["phases_ms"] = {"prefill": {k: round(v, 4) for k, v in ph.get("prefill", {}).items()},
-                            "decode_per_step": {k: round(v / 4, 4) for k, v in ph.get("decode", {}).items()}}
-        del eng
-        torch.cuda.empty_cache()
-        return res
+    measure = lambda cfg, n_layers: measure_config(cfg, vocab, T, B, toks)
 
     for name, sz in VEREDRA_SIZES.items():
         W, ff = sz["width"], sz["ff"]
@@ -753,6 +765,121 @@ def run_veredra(args) -> dict:
     return out
 
 
+SAVENEX_SIZES = {
+    # width, dense ff, experts (count, top, ff each, shared ff), left = attention (heads, kv heads, head size, window,
+    # kept first tokens), right = gated delta rule (heads, q/k heads, key size, value size, taps): two points with
+    # the layer shapes of 1-3 B and 7-8 B parameter models
+    "w2048": dict(width=2048, ff=8192, moe=(16, 2, 2048, 2048), left=(16, 4, 128, 1024, 64), right=(8, 4, 128, 256, 4)),
+    "w4096": dict(width=4096, ff=14336, moe=(16, 2, 3584, 3584), left=(32, 8, 128, 2048, 64), right=(16, 8, 128, 256, 4)),
+}
+
+
+def savenex_config(sz: dict, vocab: int) -> dict:
+    """Four layers (dense, routed, dense, routed feed-forwards); the two in the middle run twice: six layer runs."""
+    H, G, D, win, keep = sz["left"]
+    rh, rg, rk, rv, taps = sz["right"]
+    E, top, eff, sff = sz["moe"]
+    mixer = {"left": {"heads": H, "kv_heads": G, "dim": D, "vdim": D, "scale": D ** -0.5,
+                      "rot": {"base": 1e6, "dims": D, "scaling": {"factor": 2.0}},
+                      "mask": {"size": win, "keep_first": keep}},
+             "right": {"heads": rh, "kv_heads": rg, "dim": rk, "vdim": rv, "conv": taps}}
+    dense = {"kind": "dense", "ff": sz["ff"], "limit": 7.0}
+    moe = {"kind": "moe", "expert": {"ff": eff}, "router": {"experts": E, "top": top}, "shared": {"ff": sff}}
+    return {"architecture": "Savenex", "layers": [{"type": "parallel", "mixer": mixer, "mlp": m} for m in (dense, moe, dense, moe)],
+            "loop": {"start": 1, "stop": 3, "times": 2}, "norm": {"eps": 1e-6}, "residual_mult": 0.5, "vocab": vocab,
+            "width": sz["width"]}
+
+
+def veredra_pairs_config(sz: dict, vocab: int, pairs: int) -> dict:
+    """The closest model the library had: Veredra with as many (windowed attention, gated linear attention) pairs of
+    layers as Savenex has layer runs, at the same head counts, head sizes, window and feed-forward size; one residual."""
+    H, G, D, win, _ = sz["left"]
+    rh, _, rk, rv, _ = sz["right"]
+    mlp = {"kind": "dense", "ff": sz["ff"]}
+    pair = [{"type": "attention", "mixer": {"heads": H, "kv_heads": G, "dim": D, "vdim": D, "scale": D ** -0.5,
+                                            "rot": {"base": 1e6, "dims": D // 2}, "mask": {"size": win}}, "mlp": mlp},
+            {"type": "gla", "mixer": {"heads": rh, "dim": rk, "vdim": rv, "tau": 16.0}, "mlp": None}]
+    return {"architecture": "Veredra", "layers": pair * pairs, "norm": {"eps": 1e-6}, "vocab": vocab,
+            "width": sz["width"], "logit_scale": 1.0, "logit_softcap": 30.0}
+
+
+def run_savenex(args) -> dict:
+    """Prefill and decode of Savenex at two layer sizes beside Veredra (attention and gated-linear-attention layers in
+    pairs) at equal sizes, with the time of every phase per layer run that has it and each phase's share of its
+    roofline: products by flops over the measured bf16 rate in prefill and by weight bytes over the measured copy
+    rate in decode; attention by flops / cache bytes; recurrences and row kernels by bytes."""
+    import torch
+
+    pk = peaks()
+    vocab, T, B, runs = 32000, 2048, 8, 6
+    g = torch.Generator().manual_seed(7)
+    toks = lambda n: torch.randint(0, vocab, (n,), generator=g).tolist()
+    out = {"metric": "tokens/s, Savenex beside Veredra at equal layer sizes (bf16, random weights)",
+           "unit": "tokens/s", "dtype": "bf16", "data": "synthetic", "peaks": pk, "points": {}}
+    tf, bw = pk["bf16_tflops"] * 1e12, pk["hbm_gbs"] * 1e9
+    for name, sz in SAVENEX_SIZES.items():
+        W, ff = sz["width"], sz["ff"]
+        H, G, D, win, keep = sz["left"]
+        rh, rg, rk, rv, taps = sz["right"]
+        E, top, eff, sff = sz["moe"]
+        sav = measure_config(savenex_config(sz, vocab), vocab, T, B, toks)
+        ver = measure_config(veredra_pairs_config(sz, vocab, runs), vocab, T, B, toks)
+        sp, sd = sav["phases_ms"]["prefill"], sav["phases_ms"]["decode_per_step"]
+        vp, vd = ver["phases_ms"]["prefill"], ver["phases_ms"]["decode_per_step"]
+
+        def frac(ms, flops=0.0, nbytes=0.0):
+            return None if not ms else round(max(flops / tf, nbytes / bw) / (ms / 1e3), 4)
+
+        def both(sm, s_work, vm, v_work, per_s=runs, per_v=runs):
+            """{model: {prefill, decode}} for a phase (or a sum of phases) that both models have."""
+            get = lambda ph, names: sum(ph.get(n, 0) for n in names)
+            return {"savenex": {"prefill": frac(get(sp, sm) / per_s, *s_work[0]), "decode": frac(get(sd, sm) / per_s, *s_work[1])},
+                    "veredra": {"prefill": frac(get(vp, vm) / per_v, *v_work[0]), "decode": frac(get(vd, vm) / per_v, *v_work[1])}}
+
+        keys_win = sum(min(t + 1, win) for t in range(T))
+        keys_kept = sum(min(keep, max(0, t + 1 - win)) for t in range(T))
+        ctx = T - 64
+        attn_dec = lambda k: B * k * G * 2 * D * 2.0
+        s_proj = ((H + 2 * G) * D + H * D) * W + ((2 * rg * rk + rh * rv + rh + 32) * W + 16 * (rh * rk + rh * rv) + rh * rv * W)
+        v_proj = ((H + 2 * G) * D + H * D) * W + ((2 * rh * rk + 2 * rh * rv + 16) * W + 16 * rh * rk + rh * rv * W)
+        s_scan_p = T * (2 * rg * rk + rh * rk + 2 * rh * rv + rh) * 4.0
+        v_scan_p = T * (3 * rh * rk + 2 * rh * rv) * 4.0
+        state = B * rh * rk * rv * 8.0
+        dense_params, moe_flops = 3.0 * W * ff, 2.0 * T * 3.0 * W * (top * eff + sff)
+        touched = min(E, B * top) * 0.8                      # experts a decode step of B tokens reads, roughly
+        roof = {
+            "attention (window + kept first tokens / window + sink; tensor-core kernels)": both(
+                ["attention"], ((4.0 * D * H * (keys_win + keys_kept),), (0.0, attn_dec(min(ctx, win) + min(keep, max(0, ctx - win))))),
+                ["attention"], ((4.0 * D * H * keys_win,), (0.0, attn_dec(min(ctx, win))))),
+            "recurrence (gated delta rule / gated linear attention; linear_scan)": both(
+                ["scan"], ((0.0, s_scan_p), (0.0, state)), ["scan"], ((0.0, v_scan_p), (0.0, state))),
+            "mixer projections in and out": both(["qkv", "wo"], ((2.0 * T * s_proj,), (0.0, 2.0 * s_proj)),
+                                                 ["qkv", "wo"], ((2.0 * T * v_proj,), (0.0, 2.0 * v_proj))),
+            "row kernels of the mixers (rotation and cache write, convolution, unit vectors, gated norm, branch sum / the same without convolution and sum)": both(
+                ["kv_store", "conv", "gated_norm", "combine"],
+                ((0.0, T * 4.0 * ((H + 2 * G) * D * 1.5 + 4 * (2 * rg * rk + rh * rv) + 3.5 * rh * rv + 3 * W)),) * 2,
+                ["kv_store", "gated_norm"], ((0.0, T * 4.0 * ((H + 2 * G) * D * 1.5 + 3.5 * rh * rv)),) * 2),
+            "dense feed-forward (clamped gate / gelu gate)": both(
+                ["mlp"], ((2.0 * T * (dense_params + 1.5 * W * sff),), (0.0, 2.0 * (dense_params + 3.0 * W * sff))),
+                ["mlp"], ((2.0 * T * dense_params,), (0.0, 2.0 * dense_params)), per_s=runs / 2),
+            "routed experts (no like kernel in Veredra; Llama4's run the same grouped products)": {
+                "savenex": {"prefill": frac(sum(sp.get(n, 0) for n in ("moe_router", "moe_expert", "moe_merge")) / (runs / 2),
+                                            2.0 * T * 3.0 * W * top * eff),
+                            "decode": frac(sum(sd.get(n, 0) for n in ("moe_router", "moe_expert", "moe_merge")) / (runs / 2),
+                                           nbytes=2.0 * touched * 3.0 * W * eff)}},
+            "norms and the residual": both(["rmsnorm"], ((0.0, T * W * 2 * (4 + 4 + 4 + 2.0)),) * 2,
+                                           ["rmsnorm"], ((0.0, T * W * (4 + 2.0)),) * 2, per_s=runs, per_v=1.5 * runs),
+        }
+        out["points"][name] = {"sizes": sz, "layer_runs": runs, "prefill_tokens": T, "decode_batch": B, "decode_context": ctx,
+                               "savenex": sav, "veredra": ver, "fraction_of_roofline": roof}
+    big = out["points"]["w4096"]
+    out["value"] = big["savenex"]["decode_tok_s"]
+    out["config"] = {"model": "Savenex, 4 layers (attention beside a gated delta rule; dense and routed feed-forwards), "
+                              "layers 1-2 run twice", "global_batch": B, "seq_len": T, "parallelism": "single GPU",
+                     "l2": "weights of a step exceed the L2"}
+    return out
+
+
 def reference_arm_reason() -> str:
     """Why `--impl reference` has nothing to run, as found on this image (one line)."""
     return ("kurulav1/cpi is a CMake C++/CUDA project (no setup.py or pyproject.toml, so pip has nothing to install); "
@@ -772,7 +899,7 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--skip-points", action="store_true")
-    ap.add_argument("--workload", choices=["scout24", "maverick4", "long131k", "contexts", "cpu_baseline", "veredra"],
+    ap.add_argument("--workload", choices=["scout24", "maverick4", "long131k", "contexts", "cpu_baseline", "veredra", "savenex"],
                     default="scout24")
     ap.add_argument("--reference-root", default=os.environ.get("CPI_REFERENCE_ROOT"),
                     help="a checkout of kurulav1/cpi (for --workload cpu_baseline)")
@@ -789,6 +916,9 @@ def main() -> int:
     args.warmup = max(args.warmup, 3)
     if args.workload == "veredra":
         print(json.dumps(run_veredra(args)))
+        return 0
+    if args.workload == "savenex":
+        print(json.dumps(run_savenex(args)))
         return 0
     if args.workload == "contexts":
         print(json.dumps(run_contexts(args)))

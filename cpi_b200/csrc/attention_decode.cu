@@ -39,6 +39,7 @@ struct Params {
   float* part_o; float* part_ml;                    // [T, NH, splits, D], [T, NH, splits, 2]
   int* error_flag;                                  // set to 1 when a wait on the copy engine ran out
   const float* sink;                                // [NH] float32 or null: exp(sink[h]) joins the denominator
+  int keep_first;                                   // sliding window: a sequence's first positions stay visible
 };
 
 constexpr uint32_t kSpinLimit = 1u << 24;
@@ -225,14 +226,20 @@ __global__ void __launch_bounds__(NT) attention_decode_kernel(const __grid_const
   const int lo = window_low(p.window_kind, p.window_size, pos);
   const int* table = p.page_table + (size_t)slot * p.max_blocks;
   const int b_lo = lo / PAGE, b_hi = pos / PAGE;
-  const int n_blocks = b_hi - b_lo + 1;
+  // Kept first positions: the blocks that hold them and lie wholly below the window's first block come first.
+  // The splits divide the list `n_kept` kept blocks (0 .. n_kept - 1), then the window's blocks b_lo .. b_hi;
+  // item i of the list is block block_of(i).
+  const int keep = p.window_kind == 2 ? p.keep_first : 0;
+  const int n_kept = min((keep + PAGE - 1) / PAGE, b_lo);
+  const int n_blocks = n_kept + b_hi - b_lo + 1;
   const int per = (n_blocks + p.n_splits - 1) / p.n_splits;
-  const int b_begin = b_lo + split * per;
-  const int b_end = min(b_hi + 1, b_begin + per);
+  const int b_begin = split * per;
+  const int b_end = min(n_blocks, b_begin + per);
+  auto block_of = [&](int i) { return i < n_kept ? i : b_lo + i - n_kept; };
 
   // one thread asks the copy engine for the page of block `blk` into stage `st`
-  auto load_tile = [&](int blk, int st) {
-    const int row0 = (table[blk] * p.n_kv_heads + kvh) * PAGE;      // first row of the (page, head) tile
+  auto load_tile = [&](int item, int st) {
+    const int row0 = (table[block_of(item)] * p.n_kv_heads + kvh) * PAGE;      // first row of the (page, head) tile
     mbar_expect_tx(&full_bar[st], STAGE_TX);
 #pragma unroll
     for (int h = 0; h < D / 64; ++h) {
@@ -242,7 +249,7 @@ __global__ void __launch_bounds__(NT) attention_decode_kernel(const __grid_const
   };
   int asked = 0;                                                     // (thread 0) stages asked for so far
   if (tid == 0)
-    for (; asked < STAGES && b_begin + asked < b_end && b_begin + asked != b_hi; ++asked) load_tile(b_begin + asked, asked);
+    for (; asked < STAGES && b_begin + asked < b_end && block_of(b_begin + asked) != b_hi; ++asked) load_tile(b_begin + asked, asked);
   pdl_wait();
   if (tid == 0)
     for (; asked < STAGES && b_begin + asked < b_end; ++asked) load_tile(b_begin + asked, asked);
@@ -267,12 +274,14 @@ __global__ void __launch_bounds__(NT) attention_decode_kernel(const __grid_const
 #pragma unroll
   for (int i = 0; i < NO; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
 
-  for (int blk = b_begin; blk < b_end; ++blk) {
-    const int it = blk - b_begin, buf = it % STAGES;
+  for (int item = b_begin; item < b_end; ++item) {
+    const int blk = block_of(item);
+    const int it = item - b_begin, buf = it % STAGES;
     // every thread passes the barrier at the end of each round whether its wait held or not
     bool live = !*aborted;
     if (live && !mbar_wait(&full_bar[buf], (it / STAGES) & 1)) { *aborted = 1; live = false; }
-    const bool ragged = blk * PAGE < lo || blk * PAGE + PAGE - 1 > pos;      // the page holds positions outside the window
+    // the page holds positions that the query does not see
+    const bool ragged = (blk * PAGE < lo && blk * PAGE + PAGE - 1 >= keep) || blk * PAGE + PAGE - 1 > pos;
     if (live) {
     const __nv_bfloat16* kt = k_s + buf * TILE;
     __nv_bfloat16* vt = v_s + buf * TILE;
@@ -280,7 +289,7 @@ __global__ void __launch_bounds__(NT) attention_decode_kernel(const __grid_const
     if (ragged) {
       // this warp's value rows outside [lo, pos] become zeros (two lanes per row, D / 16 chunks each)
       const int row = key0 + (lane >> 1), kp = blk * PAGE + row;
-      if (kp < lo || kp > pos) {
+      if ((kp < lo && kp >= keep) || kp > pos) {
 #pragma unroll
         for (int c = 0; c < D / 16; ++c)
           *reinterpret_cast<uint4*>(vt + tile_off<D>(row, (lane & 1) * (D / 16) + c)) = make_uint4(0u, 0u, 0u, 0u);
@@ -308,7 +317,7 @@ __global__ void __launch_bounds__(NT) attention_decode_kernel(const __grid_const
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int kp = kbase + nt * 8 + (e & 1);
-        const bool valid = kp >= lo && kp <= pos;
+        const bool valid = (kp >= lo || kp < keep) && kp <= pos;
         s[nt][e] = valid ? s[nt][e] * p.scale_log2 : -INFINITY;
         mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
       }
@@ -350,7 +359,7 @@ __global__ void __launch_bounds__(NT) attention_decode_kernel(const __grid_const
     // the zeros written above must be ordered before the copy engine writes this stage again
     if (ragged) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncthreads();                                  // every warp is done with the stage: it is asked for again
-    if (tid == 0 && blk + STAGES < b_end && !*aborted) load_tile(blk + STAGES, buf);
+    if (tid == 0 && item + STAGES < b_end && !*aborted) load_tile(item + STAGES, buf);
   }
   __syncthreads();
   if (*aborted) {
@@ -454,7 +463,7 @@ extern "C" int cpi_attention_decode(const void* q, void* out, const void* k_cach
                                     const int* page_table, int max_blocks, int page_size, const int* token_seq,
                                     const int* token_pos, const int* seq_slot, int n_tokens, int n_heads,
                                     int n_kv_heads, int head_dim, int window_kind, int window_size, float scale,
-                                    int n_splits, float* part_o, float* part_ml, int* error_flag,
+                                    int n_splits, float* part_o, float* part_ml, int* error_flag, int keep_first,
                                     const float* sink, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   CPI_REQUIRE(cpi_attention_decode_supported(n_heads, n_kv_heads, head_dim, page_size),
@@ -466,7 +475,7 @@ extern "C" int cpi_attention_decode(const void* q, void* out, const void* k_cach
               "attention_decode: the cache must hold at least one page and be 16-byte aligned");
   dec::Params p{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
                 page_table, max_blocks, token_seq, token_pos, seq_slot, n_heads, n_kv_heads, window_kind, window_size,
-                scale * 1.4426950408889634f, n_splits, part_o, part_ml, error_flag, sink};
+                scale * 1.4426950408889634f, n_splits, part_o, part_ml, error_flag, sink, keep_first > 0 ? keep_first : 0};
   // the cache as rows of head_dim features: a (page, head) tile is 64 consecutive rows
   CUtensorMap mk, mv;
   const uint64_t kv_rows = (uint64_t)n_pages * n_kv_heads * dec::PAGE;
@@ -556,5 +565,5 @@ extern "C" int cpi_attention_decode_noalloc(const void* q, void* out, const void
   float* part_ml = scratch + (long)n_tokens * n_heads * n_splits * head_dim;
   return cpi_attention_decode(q, out, k_cache, v_cache, n_pages, page_table, max_blocks, page_size, token_seq,
                               token_pos, seq_slot, n_tokens, n_heads, n_kv_heads, head_dim, window_kind, window_size,
-                              scale, n_splits, part_o, part_ml, nullptr, nullptr, stream);
+                              scale, n_splits, part_o, part_ml, nullptr, 0, nullptr, stream);
 }

@@ -16,7 +16,8 @@
 // other's softmax runs; the exponentials of a tile (16,384 on 16 per cycle) take as long as its two products.
 // m is a reference maximum that is raised, and O rescaled in tensor memory, only when the row maximum
 // has outgrown it by 2^8; the division by the row sum comes once, at the end.
-// Masks: key position <= query position, and >= the window's low end (chunk or sliding window).  The
+// Masks: key position <= query position, and >= the window's low end (chunk or sliding window) or, with a
+// sliding window, below `keep_first` (a sequence's first positions that every later query still sees).  The
 // last tile's value rows beyond the newest position are zeroed in shared memory, so stale page contents
 // cannot reach the product (0 * NaN).  Formulas: src/engine/llama4_cpu_engine.cpp:195-250; the
 // reference's own prefill is a loop of single-token forwards (src/engine/llama4_cuda_engine.cu:571-580).
@@ -46,6 +47,7 @@ struct Params {
   float scale_log2;
   int* error_flag;
   const float* sink;                  // [NH] float32 or null: exp(sink[h]) joins the softmax denominator (no key, no value)
+  int keep_first;                     // sliding window: a sequence's first positions stay visible to every later query
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -241,10 +243,21 @@ __global__ void __launch_bounds__(320) attention_prefill_kernel(const __grid_con
   const int p0_x[2] = {pos_first, pos_first + BQ};                         // first position of A, of B
   const int p1_x[2] = {pos_first + rows_x[0] - 1, pos_last};               // last position of A, of B
   // key tiles (of 128 positions) that each query tile meets; the window's low end never decreases with the position
-  const int kb_x[2] = {window_low(p.window_kind, p.window_size, p0_x[0]) / BKV,
-                       has_b ? window_low(p.window_kind, p.window_size, p0_x[1]) / BKV : 0};
-  const int ke_x[2] = {p1_x[0] / BKV + 1, has_b ? p1_x[1] / BKV + 1 : 0};
-  const int kt0 = kb_x[0], kt1 = has_b ? ke_x[1] : ke_x[0];               // the union: every tile in it is met by A or B
+  const int kb_phys[2] = {window_low(p.window_kind, p.window_size, p0_x[0]) / BKV,
+                          has_b ? window_low(p.window_kind, p.window_size, p0_x[1]) / BKV : 0};
+  // Kept first positions: the key tiles that hold them and lie wholly below the window's first tile come first.
+  // The loops below count key tiles on an axis of their own, `n_kept` kept tiles (key tiles 0 .. n_kept - 1) and
+  // then the window's tiles without a gap: tile kt of the axis is key tile kt + (kt < n_kept ? 0 : gap).  With
+  // kept positions both query tiles meet every tile of the axis from its start, which always holds position 0: the
+  // second query tile sees kept positions also in the tiles between the two windows' first tiles (a tile of which
+  // it sees nothing is masked whole: at most one).
+  const int keep = p.window_kind == 2 ? p.keep_first : 0;
+  const int n_kept = min((keep + BKV - 1) / BKV, kb_phys[0]);
+  const int gap = kb_phys[0] - n_kept;
+  const int kb_x[2] = {0, has_b && keep == 0 ? kb_phys[1] - gap : 0};
+  const int ke_x[2] = {p1_x[0] / BKV + 1 - gap, has_b ? p1_x[1] / BKV + 1 - gap : 0};
+  const int kt0 = 0, kt1 = has_b ? ke_x[1] : ke_x[0];                     // the union: every tile in it is met by A or B
+  auto key_tile = [&](int kt) { return kt < n_kept ? kt : kt + gap; };
 
   if (tid == 0) {
     mbar_init(&q_full, 1);
@@ -278,7 +291,7 @@ __global__ void __launch_bounds__(320) attention_prefill_kernel(const __grid_con
       const int last_block = pos_last / PAGE;
       int n = 0;                                         // item of the ring: 2 (kt - kt0) for keys, + 1 for values
       for (int kt = kt0; kt < kt1 && ok; ++kt) {
-        const int blk0 = kt * (BKV / PAGE);
+        const int blk0 = key_tile(kt) * (BKV / PAGE);
         const int n_pages = min(BKV / PAGE, last_block - blk0 + 1);
         const uint32_t bytes = (uint32_t)n_pages * HALVES * (PAGE * 128);
         for (int which = 0; which < 2; ++which, ++n) {
@@ -398,7 +411,7 @@ __global__ void __launch_bounds__(320) attention_prefill_kernel(const __grid_con
     int j = 0;
     bool okl = rows_x[x] > 0;
     for (int kt = kb_x[x]; kt < ke_x[x] && okl; ++kt, ++j) {
-      const int key0 = kt * BKV;
+      const int key0 = key_tile(kt) * BKV;
       // (tensor-memory loads and votes are warp-wide: a warp gives up as a whole)
       okl = __all_sync(0xffffffffu, mbar_wait(&s_full[x], j & 1, abort_flag));
       if (okl && kt == kt1 - 1 && zero_duty) {
@@ -418,7 +431,7 @@ __global__ void __launch_bounds__(320) attention_prefill_kernel(const __grid_con
       if (!okl) break;
       fence_after_sync();
       // a tile that lies wholly inside every row's window needs no position tests
-      const bool no_mask = key0 + BKV - 1 <= p0_x[x] && key0 >= lo_last;
+      const bool no_mask = key0 + BKV - 1 <= p0_x[x] && (key0 >= lo_last || key0 + BKV - 1 < keep);
       // One pass over the row's 128 columns of S, 32 at a time with the next chunk's load in flight: the
       // maximum, P = 2^(s c - ref) as packed bf16, and the sum.  P is kept in registers until the pass is
       // known to stand, because it goes over the S it came from.
@@ -445,7 +458,7 @@ __global__ void __launch_bounds__(320) attention_prefill_kernel(const __grid_con
 #pragma unroll
             for (int e = 0; e < 32; ++e) {
               const int kp = key0 + cc * 32 + e;
-              const bool in = kp <= qp && kp >= lo;
+              const bool in = kp <= qp && (kp >= lo || kp < keep);
               const float sv = __uint_as_float(raw[cc & 1][e]);
               if (in) mx4[e & 3] = fmaxf(mx4[e & 3], sv);
               v[e] = in ? exp2_fast(fmaf(sv, sc, nref)) : 0.f;
@@ -549,7 +562,7 @@ extern "C" int cpi_attention_prefill(const void* q, void* out, const void* k_cac
                                      const int* token_pos, const int* seq_slot, const int* tile_tok0,
                                      const int* tile_rows, int n_tiles, int n_tokens, int n_heads, int n_kv_heads,
                                      int head_dim, int window_kind, int window_size, float scale, int* error_flag,
-                                     const float* sink, cudaStream_t stream) {
+                                     const float* sink, int keep_first, cudaStream_t stream) {
   if (n_tiles == 0) return 0;
   CPI_REQUIRE(cpi_attention_prefill_supported(n_heads, n_kv_heads, head_dim, page_size),
               "attention_prefill: unsupported shape (heads %d/%d, head size %d, page %d)", n_heads, n_kv_heads, head_dim, page_size);
@@ -562,7 +575,8 @@ extern "C" int cpi_attention_prefill(const void* q, void* out, const void* k_cac
   if (tc::get_map_2d_bf16(k_cache, (uint64_t)head_dim, kv_rows, (uint64_t)head_dim * 2, 64, pre::PAGE, &mk)) return 1;
   if (tc::get_map_2d_bf16(v_cache, (uint64_t)head_dim, kv_rows, (uint64_t)head_dim * 2, 64, pre::PAGE, &mv)) return 1;
   pre::Params p{(__nv_bfloat16*)out, page_table, max_blocks, token_pos, token_seq, seq_slot, tile_tok0, tile_rows,
-                n_heads, n_kv_heads, window_kind, window_size, scale * 1.4426950408889634f, error_flag, sink};
+                n_heads, n_kv_heads, window_kind, window_size, scale * 1.4426950408889634f, error_flag, sink,
+                keep_first > 0 ? keep_first : 0};
   dim3 grid(n_heads, n_tiles);
   const int halves = head_dim / 64;
   const int smem = halves * 128 * 128 * (2 + pre::kRingSlots);     // Q of both tiles, the ring of K and V tiles

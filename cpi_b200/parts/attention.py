@@ -197,17 +197,16 @@ class AttentionMixer(Mixer):
 
     def attend(self, q, att, k_cache, v_cache, table, page_size, batch):
         wk = K.WINDOW_KINDS[self.window_kind]
-        # the tensor-core kernels add nothing to a score, take keys and values of one size and a window without
-        # kept first positions
-        tensor_cores = (use_tensor_core_kernels and self.score_bias is None and self.dv == self.d
-                        and self.keep_first == 0)
+        # the tensor-core kernels add nothing to a score and take keys and values of one size
+        tensor_cores = use_tensor_core_kernels and self.score_bias is None and self.dv == self.d
         if (tensor_cores and batch.is_decode and q.dtype == torch.bfloat16
                 and K.attention_decode_supported(self.nh, self.nkv, self.d, page_size)):
             # keys per sequence that the window lets through, at most (a bucketed bound: the split count
             # then stays the same from step to step, which a captured graph needs)
             longest = batch.ctx_bucket
             if self.window_kind != "full":
-                longest = min(longest, self.window_size + page_size)
+                kept = -(-self.keep_first // page_size) * page_size       # the kept first positions, in whole pages
+                longest = min(longest, self.window_size + page_size + kept)
             pages = -(-longest // page_size)
             base = batch.n_tokens * self.nkv
             slots = K.attention_decode_blocks_per_sm(self.d) * K.sm_count()     # blocks that run at once
@@ -219,14 +218,14 @@ class AttentionMixer(Mixer):
             K.attention_decode(q, att, k_cache, v_cache, table, page_size, batch.token_seq, batch.token_pos,
                                batch.seq_slot, n_heads=self.nh, n_kv_heads=self.nkv, head_dim=self.d,
                                window_kind=wk, window_size=self.window_size, scale=self.scale, n_splits=n_splits,
-                               sink=self.sink)
+                               sink=self.sink, keep_first=self.keep_first)
             return
         if (tensor_cores and not batch.is_decode and q.dtype == torch.bfloat16 and batch.n_q_tiles
                 and K.attention_prefill_supported(self.nh, self.nkv, self.d, page_size)):
             K.attention_prefill(q, att, k_cache, v_cache, table, page_size, batch.token_seq, batch.token_pos,
                                 batch.seq_slot, batch.tile_tok0, batch.tile_rows, n_heads=self.nh,
                                 n_kv_heads=self.nkv, head_dim=self.d, window_kind=wk, window_size=self.window_size,
-                                scale=self.scale, sink=self.sink)
+                                scale=self.scale, sink=self.sink, keep_first=self.keep_first)
             return
         K.attention_general(q, att, k_cache, v_cache, table, page_size, batch.token_seq, batch.token_pos,
                             batch.seq_slot, n_heads=self.nh, n_kv_heads=self.nkv, head_dim=self.d,

@@ -247,6 +247,68 @@ def test_kept_first_positions_in_the_attention_kernel():
         kc[pg, 0, off] = old
 
 
+def _masked_reference(q, k, v, pos, window, keep, scale):
+    """q [NH, D] at position pos; k, v [n, NKV, D]: softmax over the keys that `P.visible` lets through."""
+    NH, G = q.shape[0], q.shape[0] // k.shape[1]
+    vis = [j for j in range(pos + 1) if P.visible(pos, j, window, keep)]
+    out = torch.empty(NH, v.shape[2], dtype=F64)
+    for h in range(NH):
+        sc = (k[vis, h // G].double() @ q[h].double()) * scale
+        out[h] = torch.softmax(sc, 0) @ v[vis, h // G].double()
+    return out
+
+
+@pytest.mark.parametrize("NH,NKV,D,window,keep", [(8, 2, 128, 130, 70), (6, 6, 64, 64, 200), (4, 1, 64, 300, 1),
+                                                  (4, 4, 128, 5, 128), (2, 1, 64, 129, 257)])
+def test_kept_first_positions_in_the_tensor_core_kernels(NH, NKV, D, window, keep):
+    """The decode kernel (one split and several) and the prefill kernel with kept first positions below a sliding
+    window: sequences shorter than the kept range, with the kept range inside the window, next to it and hundreds of
+    positions below it, kept ranges that end inside a page and inside a key tile, query tiles whose two halves'
+    windows begin in different key tiles; the general kernel on the same inputs."""
+    import test_gpu_kernels as TK
+    page, scale = 64, 1.7 / math.sqrt(D)
+    lengths = [1, 64, 65, 500, 129, 900, 258, 386]
+    k, v, table = TK.paged_cache(len(lengths), lengths, NKV, D, page, torch.bfloat16, seed=3)
+    T = len(lengths)
+    q = TK.rnd(T, NH * D, dtype=torch.bfloat16, seed=4)
+    token_seq = torch.arange(T, dtype=torch.int32, device="cuda")
+    token_pos = torch.tensor([l - 1 for l in lengths], dtype=torch.int32, device="cuda")
+    seq_slot = torch.arange(1, T + 1, dtype=torch.int32, device="cuda")
+    kw = dict(n_heads=NH, n_kv_heads=NKV, head_dim=D, window_kind=K().WINDOW_KINDS["sliding"], window_size=window,
+              scale=scale, keep_first=keep)
+    refs = []
+    for i, l in enumerate(lengths):
+        kk, vv = TK.gather_kv(k, table, i + 1, l, page), TK.gather_kv(v, table, i + 1, l, page)
+        refs.append(_masked_reference(q[i].float().view(NH, D).cpu(), kk.cpu(), vv.cpu(), l - 1, window, keep, scale).reshape(-1))
+    outs = {"general": torch.empty_like(q)}
+    K().attention_general(q, outs["general"], k, v, table, page, token_seq, token_pos, seq_slot, **kw)
+    for splits in (1, 3, 7):
+        outs[f"decode{splits}"] = torch.empty_like(q)
+        K().attention_decode(q, outs[f"decode{splits}"], k, v, table, page, token_seq, token_pos, seq_slot,
+                             n_splits=splits, **kw)
+    torch.cuda.synchronize()
+    for name, out in outs.items():
+        for i in range(T):
+            e = (out[i].double().cpu() - refs[i]).abs().max().item()
+            assert e <= 1.5e-2 * max(1.0, refs[i].abs().max().item()), (name, i, lengths[i], e)
+    c = TK._prefill_case(NH, NKV, D, ("sliding", window), [(0, 1), (0, 300), (70, 200), (100, 140), (400, 300), (0, 700),
+                                                           (513, 256), (640, 130)], tile=256)
+    out = torch.full_like(c["q"], float("nan"))
+    K().attention_prefill(c["q"], out, c["k"], c["v"], c["table"], page, c["token_seq"], c["token_pos"], c["seq_slot"],
+                          c["tile_tok0"], c["tile_rows"], **kw)
+    torch.cuda.synchronize()
+    assert int(K().tc_error_flag("cuda")[0]) == 0
+    kk = [TK.gather_kv(torch.nan_to_num(c["k"]), c["table"], i + 1, l, page).cpu() for i, l in enumerate(c["lengths"])]
+    vv = [TK.gather_kv(torch.nan_to_num(c["v"]), c["table"], i + 1, l, page).cpu() for i, l in enumerate(c["lengths"])]
+    qc = c["q"].float().cpu()
+    for t, (sq, pos) in enumerate(zip(c["seq"], c["pos"])):
+        if t % 3 and pos % 64 not in (0, 1, 63) and pos not in (keep - 1, keep, keep + window - 1, keep + window):
+            continue                                      # every third row, and every row at an edge
+        ref = _masked_reference(qc[t].view(NH, D), kk[sq], vv[sq], pos, window, keep, scale).reshape(-1)
+        e = (out[t].double().cpu() - ref).abs().max().item()
+        assert e <= 1.5e-2 * max(1.0, ref.abs().max().item()), ("prefill", t, sq, pos, e)
+
+
 def test_rotation_then_head_norm_in_the_preparation_kernel():
     g = torch.Generator().manual_seed(8)
     dev, T, H, G, D, Dv, dims, page = "cuda", 6, 3, 1, 20, 12, 8, 64
