@@ -859,8 +859,8 @@ def run_savenex(args) -> dict:
                 ["kv_store", "conv", "gated_norm", "combine"],
                 ((0.0, T * 4.0 * ((H + 2 * G) * D * 1.5 + 4 * (2 * rg * rk + rh * rv) + 3.5 * rh * rv + 3 * W)),) * 2,
                 ["kv_store", "gated_norm"], ((0.0, T * 4.0 * ((H + 2 * G) * D * 1.5 + 3.5 * rh * rv)),) * 2),
-            "dense feed-forward (clamped gate / gelu gate)": both(
-                ["mlp"], ((2.0 * T * (dense_params + 1.5 * W * sff),), (0.0, 2.0 * (dense_params + 3.0 * W * sff))),
+            "dense feed-forward and the shared expert (clamped and silu gates / gelu gate)": both(
+                ["mlp"], ((2.0 * T * (dense_params + 3.0 * W * sff),), (0.0, 2.0 * (dense_params + 3.0 * W * sff))),
                 ["mlp"], ((2.0 * T * dense_params,), (0.0, 2.0 * dense_params)), per_s=runs / 2),
             "routed experts (no like kernel in Veredra; Llama4's run the same grouped products)": {
                 "savenex": {"prefill": frac(sum(sp.get(n, 0) for n in ("moe_router", "moe_expert", "moe_merge")) / (runs / 2),

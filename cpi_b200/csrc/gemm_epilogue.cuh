@@ -30,8 +30,10 @@ __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(
 // act(g) * u for the gate activations the fused epilogues know: 0 silu, 1 the tanh form of gelu,
 // 0.5 g (1 + tanh(c (g + 0.044715 g^3))) = g * sigmoid(2 c (g + 0.044715 g^3)) with c = sqrt(2 / pi): the same two
 // special-function instructions as silu and three more multiplies, chosen without a branch.
-__device__ __forceinline__ float gate_mul(float g, float u, int act) {
-  const float inner = act ? 1.5957691216057308f * fmaf(0.044715f * g * g, g, g) : g;
+// 2 the clamped form: g' = min(g, limit), u' = clamp(u, -limit, limit), g' * sigmoid(1.702 g') * (u' + 1).
+__device__ __forceinline__ float gate_mul(float g, float u, int act, float limit = 0.f) {
+  if (act == 2) { g = fminf(g, limit); u = fminf(fmaxf(u, -limit), limit) + 1.0f; }
+  const float inner = act == 1 ? 1.5957691216057308f * fmaf(0.044715f * g * g, g, g) : act == 2 ? 1.702f * g : g;
   return __fdividef(g, 1.0f + __expf(-inner)) * u;
 }
 
@@ -76,7 +78,7 @@ template <int ID, int THREADS> struct NamedSync {
 template <int MODE, typename TO, int STAGE_COLS, typename Ld, typename LdU, typename Sync = CtaSync>
 __device__ __forceinline__ void staged(void* stage_mem, Ld ld16, LdU ld16u, int warp, int lane, int n0, int N, int t0,
                                        int n_valid_t, int n_cols, TO* out, long ldo, const int* out_rows,
-                                       const float* row_scale, Sync sync = Sync(), int gate_act = 0) {
+                                       const float* row_scale, Sync sync = Sync(), int gate_act = 0, float gate_limit = 0.f) {
   static_assert(STAGE_COLS >= 16 && STAGE_COLS % 16 == 0, "the stage holds whole chunks of 16 columns");
   using S = typename Stage<TO>::T;
   S* stage = reinterpret_cast<S*>(stage_mem);
@@ -108,7 +110,7 @@ __device__ __forceinline__ void staged(void* stage_mem, Ld ld16, LdU ld16u, int 
     for (int j = 0; j < 16; ++j) {
       const float s = scale ? scale[min(c + j, n_valid_t - 1)] : 1.0f;
       float x = v[j] * s;
-      if (MODE == kSwiglu) x = gate_mul(x, u[j] * s, gate_act);
+      if (MODE == kSwiglu) x = gate_mul(x, u[j] * s, gate_act, gate_limit);
       v[j] = x;
     }
 #pragma unroll

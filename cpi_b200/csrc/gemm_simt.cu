@@ -25,7 +25,8 @@ struct GemmParams {
   const float* row_scale;
   const int* group_offsets; int n_groups;
   int M, N, K;
-  int gate_act;      // gated mode: the gate's activation (0 silu, 1 gelu in its tanh form)
+  int gate_act;      // gated mode: the gate's activation (0 silu, 1 gelu in its tanh form, 2 the clamped form below)
+  float gate_limit;  // act 2: g' = min(g, limit), u' = clamp(u, -limit, limit), out = g' sigmoid(1.702 g') (u' + 1)
 };
 
 constexpr int BN = 64, BK = 16, NT = 256;
@@ -126,9 +127,15 @@ __global__ void __launch_bounds__(NT) gemm_simt_kernel(GemmParams p) {
       if (n >= p.N) continue;
       float v = acc[i][j] * s;
       if (MODE == kSwiglu) {
-        const float u = acc2[i][j] * s;
-        v = (p.gate_act ? 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)))
-                        : v / (1.0f + expf(-v))) * u;
+        float u = acc2[i][j] * s;
+        if (p.gate_act == 2) {
+          v = fminf(v, p.gate_limit);
+          u = fminf(fmaxf(u, -p.gate_limit), p.gate_limit) + 1.0f;
+          v = v / (1.0f + expf(-1.702f * v)) * u;
+        } else {
+          v = (p.gate_act ? 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)))
+                          : v / (1.0f + expf(-v))) * u;
+        }
         o[n] = from_f32<TO>(v);
       } else if (MODE == kAdd) {
         o[n] = from_f32<TO>(to_f32(o[n]) + v);
@@ -174,14 +181,15 @@ extern "C" int cpi_gemm_simt(const void* a, int a_dtype, long lda, const int* a_
                              const void* w, int w_dtype, long ldw, long w_group_stride,
                              void* out, int out_dtype, long ldo, const int* out_rows,
                              const float* row_scale, const int* group_offsets, int n_groups,
-                             int M, int N, int K, int mode, int rows_per_group_hint, cudaStream_t stream) {
+                             int M, int N, int K, int mode, int rows_per_group_hint, float gate_limit,
+                             cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
-  const int gate_act = mode == 3 ? 1 : 0;          // mode 3: the gated mode with a gelu gate
-  if (mode == 3) mode = 2;
+  const int gate_act = mode == 3 ? 1 : mode == 4 ? 2 : 0;      // modes 3, 4: the gated mode with a gelu / a clamped gate
+  if (mode == 3 || mode == 4) mode = 2;
   CPI_REQUIRE(M > 0 && N > 0 && K > 0, "gemm: bad sizes M=%d N=%d K=%d", M, N, K);
   CPI_REQUIRE(mode != kAdd || out_dtype == kF32, "gemm: ADD mode needs a float32 output");
   GemmParams p{a, lda, a_rows, w, ldw, w_group_stride, out, ldo, out_rows, row_scale,
-               group_offsets, n_groups, M, N, K, gate_act};
+               group_offsets, n_groups, M, N, K, gate_act, gate_limit};
   CPI_DISPATCH_DTYPE(a_dtype, TA, CPI_DISPATCH_DTYPE(w_dtype, TW, CPI_DISPATCH_DTYPE(out_dtype, TO,
       return (launch_mode<TA, TW, TO>(p, mode, rows_per_group_hint, stream)))));
   return 0;

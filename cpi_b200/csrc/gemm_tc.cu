@@ -57,7 +57,8 @@ struct Params {
   int* error_flag;
   uint32_t spin_limit; // polls of one barrier wait before the CTA gives up
   uint32_t tx_extra;   // bytes added to what a stage's barrier expects (0 but in the test of the give-up path)
-  int gate_act;        // gated mode: the gate's activation (0 silu, 1 gelu in its tanh form)
+  int gate_act;        // gated mode: the gate's activation (0 silu, 1 gelu in its tanh form, 2 clamped: see gate_mul)
+  float gate_limit;    // the clamp of act 2
 };
 
 // ---------------------------------------------------------------------------------------------- PTX
@@ -312,7 +313,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
     TO* o = out + (size_t)(p.out_rows ? p.out_rows[lr] : lr) * p.ldo + n;
     if (MODE == kSwiglu) {
       u *= s;
-      store_out<TO>(o, epi::gate_mul(v, u, p.gate_act));
+      store_out<TO>(o, epi::gate_mul(v, u, p.gate_act, p.gate_limit));
     } else if (MODE == kAdd) {
       store_out<TO>(o, to_f32(*o) + v);
     } else {
@@ -328,7 +329,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
       constexpr int kStageCols = kFit < BN ? kFit : BN;
       auto ld = [&](int c, float* d) { tmem_ld16(lane_addr + c, d); };
       auto ldu = [&](int c, float* d) { tmem_ld16(lane_addr + BN + c, d); };
-      epi::staged<MODE, TO, kStageCols>(smem, ld, ldu, warp, lane, n0, p.N, t0, n_valid_t, n_cols, out, p.ldo, p.out_rows, p.row_scale, epi::CtaSync(), p.gate_act);
+      epi::staged<MODE, TO, kStageCols>(smem, ld, ldu, warp, lane, n0, p.N, t0, n_valid_t, n_cols, out, p.ldo, p.out_rows, p.row_scale, epi::CtaSync(), p.gate_act, p.gate_limit);
     } else if (MODE == kAdd) {
       // read-modify-write of the residual: the old values of chunk c+1 are fetched while chunk c is added,
       // so that their latency hides behind the tensor-memory load
@@ -695,11 +696,11 @@ extern "C" int cpi_gemm_tc_plan(int T, int N, int K, int n_groups, int swiglu, i
 // `bn` and `splits` as cpi_gemm_tc_plan gives them (splits > 1 only with a power-of-two token tile up to 128).
 extern "C" int cpi_gemm_tc(const void* x, long ldx, const void* w, void* out, int out_dtype, long ldo,
                            const int* out_rows, const float* row_scale, const int* group_offsets, int n_groups,
-                           int T, int N, int K, int mode, int bn, int splits, int* error_flag,
+                           int T, int N, int K, int mode, int bn, int splits, int* error_flag, float gate_limit,
                            cudaStream_t stream) {
   if (T == 0 || N == 0) return 0;
-  const int gate_act = mode == 3 ? 1 : 0;          // mode 3: the gated mode with a gelu gate
-  if (mode == 3) mode = 2;
+  const int gate_act = mode == 3 ? 1 : mode == 4 ? 2 : 0;      // modes 3, 4: the gated mode with a gelu / a clamped gate
+  if (mode == 3 || mode == 4) mode = 2;
   CPI_REQUIRE(T > 0 && N > 0 && K > 0, "gemm_tc: bad sizes T=%d N=%d K=%d", T, N, K);
   CPI_REQUIRE(K % 8 == 0 && ldx % 8 == 0, "gemm_tc: K (%d) and the activation row stride (%ld) must be multiples of 8", K, ldx);
   CPI_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0,
@@ -729,7 +730,7 @@ extern "C" int cpi_gemm_tc(const void* x, long ldx, const void* w, void* out, in
   // one-accumulator product, whose token rows are the larger operand)
   const int tiles_on_x = mode == tc::kSwiglu && n_groups > 0 && T > 2 * n_groups && splits == 1 && grid.x <= 65535;
   if (tiles_on_x) { const unsigned gx = grid.x; grid.x = grid.y; grid.y = gx; }
-  tc::Params p{out, ldo, out_rows, row_scale, group_offsets, n_groups, T, bn, N, k_tiles, splits, per, tiles_on_x, error_flag, g_spin_limit, g_tx_extra, gate_act};
+  tc::Params p{out, ldo, out_rows, row_scale, group_offsets, n_groups, T, bn, N, k_tiles, splits, per, tiles_on_x, error_flag, g_spin_limit, g_tx_extra, gate_act, gate_limit};
   if (mode == tc::kStore && out_dtype == kBF16) return tc::launch_bn<tc::kStore, __nv_bfloat16>(cap, mw, mx, p, grid, stream);
   if (mode == tc::kStore && out_dtype == kF32) return tc::launch_bn<tc::kStore, float>(cap, mw, mx, p, grid, stream);
   if (mode == tc::kAdd) return tc::launch_bn<tc::kAdd, float>(cap, mw, mx, p, grid, stream);

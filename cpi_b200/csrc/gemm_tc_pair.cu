@@ -42,7 +42,8 @@ struct Params {
   const int* group_offsets; int n_groups;      // routed experts: tokens [offsets[g], offsets[g+1]) use W[g]
   int T, bn, N, k_tiles;
   int* error_flag;
-  int gate_act;                                // gated mode: the gate's activation (0 silu, 1 gelu in its tanh form)
+  int gate_act;                                // gated mode: the gate's activation (0 silu, 1 gelu in its tanh form, 2 clamped)
+  float gate_limit;                            // the clamp of act 2 (see epi::gate_mul)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -276,7 +277,7 @@ __global__ void __launch_bounds__(128) gemm_tc_pair_kernel(const __grid_constant
       constexpr int kStageCols = kFit < BN ? kFit : BN;
       auto ld = [&](int c, float* d) { tmem_ld16(lane_addr + c, d); };
     auto ldu = [&](int c, float* d) { tmem_ld16(lane_addr + BN + c, d); };
-    epi::staged<MODE, TO, kStageCols>(smem, ld, ldu, warp, lane, n0, p.N, t0, n_valid_t, n_cols, out, p.ldo, p.out_rows, p.row_scale, epi::CtaSync(), p.gate_act);
+    epi::staged<MODE, TO, kStageCols>(smem, ld, ldu, warp, lane, n0, p.N, t0, n_valid_t, n_cols, out, p.ldo, p.out_rows, p.row_scale, epi::CtaSync(), p.gate_act, p.gate_limit);
   } else if (ok && MODE == kAdd) {
     float* outf = reinterpret_cast<float*>(p.out);
     float old[2][16];
@@ -319,7 +320,7 @@ __global__ void __launch_bounds__(128) gemm_tc_pair_kernel(const __grid_constant
         if (!row_ok || col >= n_valid_t) continue;
         const float s = p.row_scale ? p.row_scale[t0 + col] : 1.0f;
         float x = v[j] * s;
-        if (MODE == kSwiglu) x = epi::gate_mul(x, u[j] * s, p.gate_act);
+        if (MODE == kSwiglu) x = epi::gate_mul(x, u[j] * s, p.gate_act, p.gate_limit);
         store_out<TO>(out + (size_t)(p.out_rows ? p.out_rows[t0 + col] : t0 + col) * p.ldo + n, x);
       }
     }
@@ -517,7 +518,7 @@ __global__ void __launch_bounds__(192) gemm_tc_pair_persistent_kernel(const __gr
       auto ldu = [&](int c, float* d) { tmem_ld16(lane_addr + BN + c, d); };
       TO* out = reinterpret_cast<TO*>(p.out);
       epi::staged<MODE, TO, EPI_COLS>(epi, ld, ldu, warp, lane, n0, p.N, t0, n_valid_t, n_cols, out, p.ldo, p.out_rows,
-                                      p.row_scale, epi::NamedSync<1, 128>(), p.gate_act);
+                                      p.row_scale, epi::NamedSync<1, 128>(), p.gate_act, p.gate_limit);
       // the accumulator has been read (the last tensor-memory load of the tile precedes the last barrier above)
       fence_before_sync();
       __syncwarp();
@@ -657,10 +658,11 @@ extern "C" int cpi_gemm_tc_pair_plan(int T, int N, int K, int swiglu, int n_grou
 // x [T, K] bf16 (row stride ldx), w [N or 2N][K] bf16 contiguous, out [T, N]; bn from cpi_gemm_tc_pair_plan.
 extern "C" int cpi_gemm_tc_pair(const void* x, long ldx, const void* w, void* out, int out_dtype, long ldo,
                                 const int* out_rows, const float* row_scale, const int* group_offsets, int n_groups,
-                                int T, int N, int K, int mode, int bn, int* error_flag, cudaStream_t stream) {
+                                int T, int N, int K, int mode, int bn, int* error_flag, float gate_limit,
+                                cudaStream_t stream) {
   if (T == 0 || N == 0) return 0;
-  const int gate_act = mode == 3 ? 1 : 0;          // mode 3: the gated mode with a gelu gate
-  if (mode == 3) mode = 2;
+  const int gate_act = mode == 3 ? 1 : mode == 4 ? 2 : 0;      // modes 3, 4: the gated mode with a gelu / a clamped gate
+  if (mode == 3 || mode == 4) mode = 2;
   CPI_REQUIRE(N % 256 == 0 && K % 8 == 0 && ldx % 8 == 0, "gemm_tc_pair: N (%d) must be a multiple of 256, K (%d) and the row stride of 8", N, K);
   CPI_REQUIRE(bn >= 32 && bn <= 256 && bn % 32 == 0, "gemm_tc_pair: token tile %d (multiples of 32 up to 256)", bn);
   CPI_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0, "gemm_tc_pair: operands must be 16-byte aligned");
@@ -671,7 +673,7 @@ extern "C" int cpi_gemm_tc_pair(const void* x, long ldx, const void* w, void* ou
   CPI_REQUIRE(n_groups <= 256, "gemm_tc_pair: %d groups (at most 256)", n_groups);
   if (tc::get_map_3d_bf16(w, (uint64_t)K, (uint64_t)acc * N, (uint64_t)(n_groups > 0 ? n_groups : 1), tc2::BK, tc2::BM, &mw)) return 1;
   if (tc::get_map_2d_bf16(x, (uint64_t)K, (uint64_t)T, (uint64_t)ldx * 2, tc2::BK, 64, &mx)) return 1;
-  tc2::Params p{out, ldo, out_rows, row_scale, group_offsets, n_groups, T, bn, N, (K + tc2::BK - 1) / tc2::BK, error_flag, gate_act};
+  tc2::Params p{out, ldo, out_rows, row_scale, group_offsets, n_groups, T, bn, N, (K + tc2::BK - 1) / tc2::BK, error_flag, gate_act, gate_limit};
   dim3 grid(N / tc2::BM, (T + bn - 1) / bn + (n_groups > 0 ? (T < n_groups ? T : n_groups) : 0), 1);
   CPI_REQUIRE(grid.y <= 65535, "gemm_tc_pair: too many token tiles (%u)", grid.y);
   const int cap = bn <= 128 ? 128 : 256;

@@ -14,7 +14,8 @@ from . import build as _build
 
 F32, BF16 = 0, 1
 MODE_STORE, MODE_ADD, MODE_SWIGLU, MODE_GEGLU = 0, 1, 2, 3      # GEGLU: the gated mode with a gelu (tanh form) gate
-GATED_MODES = (MODE_SWIGLU, MODE_GEGLU)
+MODE_CLAMPED_GLU = 4             # the gated mode with g' = min(g, limit), u' = clamp(u, -limit, limit), g' sigmoid(1.702 g') (u' + 1)
+GATED_MODES = (MODE_SWIGLU, MODE_GEGLU, MODE_CLAMPED_GLU)
 WINDOW_FULL, WINDOW_CHUNK, WINDOW_SLIDING = 0, 1, 2
 WINDOW_KINDS = {"full": WINDOW_FULL, "chunk": WINDOW_CHUNK, "sliding": WINDOW_SLIDING}
 MAX_DECODE_SPLITS = 256          # key splits that the combine kernel of decode attention takes
@@ -113,7 +114,7 @@ def rmsnorm(x, weight, eps, out, rows=None, weight_offset=0.0):
 
 
 def gemm_simt(a, w, out, mode=MODE_STORE, *, n_out=None, m_rows=None, a_rows=None, out_rows=None,
-              row_scale=None, group_offsets=None, n_groups=0, rows_per_group_hint=None):
+              row_scale=None, group_offsets=None, n_groups=0, rows_per_group_hint=None, gate_limit=0.0):
     """out[m, n] (+)= sum_k a[a_rows[m] or m, k] * w[g(m)][n, k] on the FP32 pipe (see gemm_simt.cu).
 
     w is [N, K], or [2N, K] in SWIGLU mode, or [G, N or 2N, K] with group_offsets (int32 [G+1]).
@@ -137,7 +138,8 @@ def gemm_simt(a, w, out, mode=MODE_STORE, *, n_out=None, m_rows=None, a_rows=Non
     _call("cpi_gemm_simt", _p(a), c_int(dtype_code(a.dtype)), c_long(a.stride(0)), _p(a_rows),
           _p(w), c_int(dtype_code(w.dtype)), c_long(ldw), c_long(stride_g),
           _p(out), c_int(dtype_code(out.dtype)), c_long(out.stride(0)), _p(out_rows), _p(row_scale),
-          _p(group_offsets), c_int(n_groups), c_int(M), c_int(N), c_int(K), c_int(mode), c_int(hint), _stream())
+          _p(group_offsets), c_int(n_groups), c_int(M), c_int(N), c_int(K), c_int(mode), c_int(hint),
+          c_float(gate_limit), _stream())
 
 
 _errors = {}          # device index -> int32[2]: [0] a tensor-core kernel gave up a wait, [1] a token id out of range
@@ -164,7 +166,7 @@ def sm_count() -> int:
 
 
 def gemm_tc(a, w, out, mode=MODE_STORE, *, n_out=None, m_rows=None, a_rows=None, out_rows=None, row_scale=None,
-            group_offsets=None, n_groups=0, rows_per_group_hint=None) -> bool:
+            group_offsets=None, n_groups=0, rows_per_group_hint=None, gate_limit=0.0) -> bool:
     """The tcgen05 kernel for out[m, n] (+)= sum_k a[m, k] w[g(m)][n, k] in bfloat16 (see gemm_tc.cu).
 
     Returns False, having launched nothing, when the call is outside what the kernel takes (a row
@@ -199,7 +201,7 @@ def gemm_tc(a, w, out, mode=MODE_STORE, *, n_out=None, m_rows=None, a_rows=None,
     _call("cpi_gemm_tc", _p(a), c_long(a.stride(0)), _p(w), _p(out), c_int(dtype_code(out.dtype)),
           c_long(out.stride(0)), _p(out_rows), _p(row_scale), _p(group_offsets), c_int(n_groups if grouped else 0),
           c_int(T), c_int(N), c_int(K), c_int(mode), c_int(bn.value), c_int(splits.value),
-          _p(tc_error_flag(a.device)), _stream())
+          _p(tc_error_flag(a.device)), c_float(gate_limit), _stream())
     return True
 
 
@@ -226,7 +228,7 @@ def gemm_pair_persistent(mode) -> None:
 
 
 def gemm_tc_pair(a, w, out, mode=MODE_STORE, *, m_rows=None, out_rows=None, row_scale=None, group_offsets=None,
-                 n_groups=0, rows_per_group_hint=None) -> bool:
+                 n_groups=0, rows_per_group_hint=None, gate_limit=0.0) -> bool:
     """The paired (two-SM) tcgen05 kernel for products with many tokens, dense or grouped (see
     gemm_tc_pair.cu).  Returns False, having launched nothing, when the product is outside what it takes."""
     grouped = group_offsets is not None
@@ -251,7 +253,8 @@ def gemm_tc_pair(a, w, out, mode=MODE_STORE, *, m_rows=None, out_rows=None, row_
     _need_cuda(a, w, out, out_rows, row_scale, group_offsets)
     _call("cpi_gemm_tc_pair", _p(a), c_long(a.stride(0)), _p(w), _p(out), c_int(dtype_code(out.dtype)),
           c_long(out.stride(0)), _p(out_rows), _p(row_scale), _p(group_offsets), c_int(n_groups if grouped else 0),
-          c_int(T), c_int(N), c_int(K), c_int(mode), c_int(bn), _p(tc_error_flag(a.device)), _stream())
+          c_int(T), c_int(N), c_int(K), c_int(mode), c_int(bn), _p(tc_error_flag(a.device)), c_float(gate_limit),
+          _stream())
     return True
 
 
@@ -607,7 +610,22 @@ def router_topk(h, w, topk_idx, topk_gate, *, top_k, sigmoid_gate, logits_out=No
         n = min(65535, T - t0)
         _call("cpi_router_topk", _p(h[t0:t0 + n]), c_int(dtype_code(h.dtype)), c_long(h.stride(0)), _p(w),
               c_int(dtype_code(w.dtype)), _p(logits_out[t0:t0 + n]), _p(topk_idx[t0:t0 + n]), _p(topk_gate[t0:t0 + n]),
-              c_int(n), c_int(H), c_int(E), c_int(top_k), c_int(_gate_mode(sigmoid_gate)), _p(bias), _stream())
+              c_int(n), c_int(H), c_int(E), c_int(top_k), c_int(_gate_mode(sigmoid_gate)), _p(bias), c_int(0), _stream())
+
+
+def row_gates(h, w, out, bias=None):
+    """out[t, e] = sigmoid(h[t] . w[e] (+ bias[e])) in float32, the router's dot products in one launch: a gate per
+    token and row of w (w [E, H], out float32 [T, E])."""
+    _need_cuda(h, w, out, bias)
+    _rowmajor(h, "row_gates h")
+    T, H = h.shape
+    E = w.shape[0]
+    assert w.is_contiguous() and w.shape[1] == H and out.dtype == torch.float32 and out.is_contiguous() and out.numel() == T * E
+    for t0 in range(0, T, 65535):
+        n = min(65535, T - t0)
+        _call("cpi_router_topk", _p(h[t0:t0 + n]), c_int(dtype_code(h.dtype)), c_long(h.stride(0)), _p(w),
+              c_int(dtype_code(w.dtype)), _p(out.view(T, E)[t0:t0 + n]), None, None, c_int(n), c_int(H), c_int(E), c_int(1),
+              c_int(0), _p(bias), c_int(1), _stream())
 
 
 def moe_route(h, w, topk_idx, topk_gate, logits, group_offsets, row_token, row_scale, row_of_slot, *, top_k,
@@ -626,7 +644,7 @@ def moe_route(h, w, topk_idx, topk_gate, logits, group_offsets, row_token, row_s
         assert w.is_contiguous() and w.shape[1] == H and logits.dtype == torch.float32 and logits.is_contiguous()
         _call("cpi_router_topk", _p(h), c_int(dtype_code(h.dtype)), c_long(h.stride(0)), _p(w),
               c_int(dtype_code(w.dtype)), _p(logits), None, None, c_int(T), c_int(H), c_int(E), c_int(top_k),
-              c_int(gm), _p(bias), _stream())
+              c_int(gm), _p(bias), c_int(0), _stream())
         rc = load().cpi_moe_route_small(_p(logits), c_int(T), c_int(E), c_int(top_k), c_int(gm),
                                         _p(topk_idx), _p(topk_gate), _p(group_offsets), _p(row_token), _p(row_scale),
                                         _p(row_of_slot), _p(h), c_long(h.stride(0) * h.element_size()), _p(sorted_h),

@@ -38,7 +38,8 @@ template <typename T> __device__ __forceinline__ void load_group(const T* row, i
 template <typename TH, typename TW>
 __global__ void __launch_bounds__(128)
 router_logits_kernel(const TH* __restrict__ h, long h_stride, const TW* __restrict__ w,
-                     float* __restrict__ logits, int hidden, int n_experts, int vec, const float* __restrict__ bias) {
+                     float* __restrict__ logits, int hidden, int n_experts, int vec, const float* __restrict__ bias,
+                     int sigmoid_out) {
   pdl_launch_dependents();
   __shared__ float scratch[32];
   const int e = blockIdx.x, t = blockIdx.y;
@@ -77,7 +78,10 @@ router_logits_kernel(const TH* __restrict__ h, long h_stride, const TW* __restri
     }
   }
   s = block_sum(s, scratch);
-  if (threadIdx.x == 0) logits[(size_t)t * n_experts + e] = bias ? s + bias[e] : s;
+  if (threadIdx.x == 0) {
+    if (bias) s += bias[e];
+    logits[(size_t)t * n_experts + e] = sigmoid_out ? 1.0f / (1.0f + expf(-s)) : s;
+  }
 }
 
 // A block takes TOK tokens and EXP experts at a time -- for many tokens: every loaded activation is used
@@ -86,7 +90,7 @@ template <typename TH, typename TW, int TOK, int EXP>
 __global__ void __launch_bounds__(128)
 router_logits_tile_kernel(const TH* __restrict__ h, long h_stride, const TW* __restrict__ w,
                           float* __restrict__ logits, int n_tokens, int hidden, int n_experts, int vec,
-                          const float* __restrict__ bias) {
+                          const float* __restrict__ bias, int sigmoid_out) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float part[4][TOK * EXP];
@@ -126,7 +130,8 @@ router_logits_tile_kernel(const TH* __restrict__ h, long h_stride, const TW* __r
     if (t0 + a < n_tokens && e0 + b < n_experts) {
       float r = 0.f;
       for (int wq = 0; wq < 4; ++wq) r += part[wq][k];
-      logits[(size_t)(t0 + a) * n_experts + e0 + b] = bias ? r + bias[e0 + b] : r;
+      if (bias) r += bias[e0 + b];
+      logits[(size_t)(t0 + a) * n_experts + e0 + b] = sigmoid_out ? 1.0f / (1.0f + expf(-r)) : r;
     }
   }
 }
@@ -300,15 +305,17 @@ using namespace cpi;
 
 // gate_mode: 0 none (gates are 1), 1 sigmoid of the chosen logit, 2 softmax over the chosen logits.  `logits` is
 // float32 [n_tokens, n_experts] scratch that also serves as the optional output of the router logits; `bias`
-// (float32 [n_experts] or null) is added to them.
+// (float32 [n_experts] or null) is added to them.  `sigmoid_out` (only without a selection, topk_idx null): what is
+// written is the sigmoid of each logit -- a gate per token and row of `w`, in one launch.
 extern "C" int cpi_router_topk(const void* h, int h_dtype, long h_stride, const void* w, int w_dtype,
                                float* logits, int* topk_idx, float* topk_gate, int n_tokens,
                                int hidden, int n_experts, int top_k, int gate_mode, const float* bias,
-                               cudaStream_t stream) {
+                               int sigmoid_out, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   CPI_REQUIRE(n_experts >= 1 && n_experts <= kMaxExperts, "router: %d experts (supported: 1..%d)", n_experts, kMaxExperts);
   CPI_REQUIRE(top_k >= 1 && top_k <= n_experts, "router: top-k %d of %d experts", top_k, n_experts);
   CPI_REQUIRE(logits != nullptr, "router: the logits buffer is missing");
+  CPI_REQUIRE(!sigmoid_out || topk_idx == nullptr, "router: sigmoid_out writes gates instead of logits; nothing can be selected from them");
   CPI_REQUIRE(n_tokens <= 65535, "router: too many tokens in one launch (%d)", n_tokens);
   const int esz_h = h_dtype == kF32 ? 4 : 2, esz_w = w_dtype == kF32 ? 4 : 2;
   const int vec = hidden % 8 == 0 && (h_stride * esz_h) % 16 == 0 && (reinterpret_cast<uintptr_t>(h) & 15) == 0 &&
@@ -317,11 +324,11 @@ extern "C" int cpi_router_topk(const void* h, int h_dtype, long h_stride, const 
     constexpr int TOK = 4, EXP = 4;
     dim3 grid((n_tokens + TOK - 1) / TOK, (n_experts + EXP - 1) / EXP);
     CPI_DISPATCH_DTYPE(h_dtype, TH, CPI_DISPATCH_DTYPE(w_dtype, TW,
-        (cpi::launch_pdl(router_logits_tile_kernel<TH, TW, TOK, EXP>, grid, 128, 0, stream, (const TH*)h, h_stride, (const TW*)w, logits, n_tokens, hidden, n_experts, vec, bias))));
+        (cpi::launch_pdl(router_logits_tile_kernel<TH, TW, TOK, EXP>, grid, 128, 0, stream, (const TH*)h, h_stride, (const TW*)w, logits, n_tokens, hidden, n_experts, vec, bias, sigmoid_out))));
   } else {
     dim3 grid(n_experts, n_tokens);
     CPI_DISPATCH_DTYPE(h_dtype, TH, CPI_DISPATCH_DTYPE(w_dtype, TW,
-        (cpi::launch_pdl(router_logits_kernel<TH, TW>, grid, 128, 0, stream, (const TH*)h, h_stride, (const TW*)w, logits, hidden, n_experts, vec, bias))));
+        (cpi::launch_pdl(router_logits_kernel<TH, TW>, grid, 128, 0, stream, (const TH*)h, h_stride, (const TW*)w, logits, hidden, n_experts, vec, bias, sigmoid_out))));
   }
   if (check_launch("router_logits")) return 2;
   if (!topk_idx) return 0;                          // logits only: the caller selects in a later kernel

@@ -120,7 +120,9 @@ struct RowDecayParams {
 // z[t, i] <- sigmoid(z[t, i] + bias[i])^(1 / tau), in place: the decays of a step of many tokens, once per element
 // instead of once per block of columns inside the recurrence
 __global__ void __launch_bounds__(256) row_decay_kernel(RowDecayParams p) {
-  pdl_launch_dependents();
+  // (no early launch of the kernel behind it: that is the recurrence of a prompt, whose few blocks would be placed
+  // on whichever multiprocessors this kernel's blocks leave first, several to one, instead of one each; measured:
+  // 1.09 instead of 0.60 ms for the delta rule at 2,048 tokens)
   pdl_wait();
   const int i = blockIdx.y * blockDim.x + threadIdx.x;
   if (i >= p.n) return;
@@ -148,7 +150,10 @@ template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile(
 // so that the 16-byte reads of different kk fall into different banks.
 template <int NPT, int KS, bool ROW_DECAY, int CPT, bool DELTA>
 __global__ void __launch_bounds__(256) linear_scan_kernel(ScanParams p) {
-  pdl_launch_dependents();
+  // A decode step (one token staged at a time) lets the kernel behind it start at once.  A prompt does not: its few
+  // blocks run for hundreds of microseconds, one to a multiprocessor, on a chain of dependent instructions, and
+  // thousands of blocks of the next kernel waiting beside them were measured to slow that chain by half.
+  if (p.chunk == 1) pdl_launch_dependents();
   extern __shared__ __align__(16) float smem[];
   constexpr int PVW = 32 / KS, ROWP = KS * (NPT + 4), NVEC = ROW_DECAY ? 3 : 2;
   const int nwarps = blockDim.x >> 5, pvb = nwarps * PVW * CPT;
@@ -284,47 +289,59 @@ __global__ void __launch_bounds__(256) linear_scan_kernel(ScanParams p) {
         o2[c] = make_float2(0.f, 0.f);
       }
       if constexpr (DELTA) {
-        // the delta rule: decay, then what the state already answers to this key, then the corrected write
-        float2 d2[CPT];
+        // The delta rule.  One pass over the thread's rows decays them and takes, for every column, what the decayed
+        // state answers to this token's key (d) and to its query (e), and once per thread its share of k . q.  After
+        // the sums over the lanes that share a column, u = beta (v - d) is what the token writes, and its output is
+        // S'^T q = e + (k . q) u: the read-out of the updated state without a second sum over it.  The second pass
+        // only adds k u^T to the rows.
+        float2 d2[CPT], kq2 = make_float2(0.f, 0.f);
 #pragma unroll
         for (int c = 0; c < CPT; ++c) d2[c] = make_float2(0.f, 0.f);
 #pragma unroll
         for (int i4 = 0; i4 < NPT / 4; ++i4) {
-          const float4 kq = k4[i4];
+          const float4 kq = k4[i4], qq = q4[i4];
           float4 dd = make_float4(a, a, a, a);
           if (ROW_DECAY) dd = d4[i4];
           const float2 kr[2] = {make_float2(kq.x, kq.y), make_float2(kq.z, kq.w)};
+          const float2 qr[2] = {make_float2(qq.x, qq.y), make_float2(qq.z, qq.w)};
           const float2 dr[2] = {make_float2(dd.x, dd.y), make_float2(dd.z, dd.w)};
 #pragma unroll
           for (int r = 0; r < 2; ++r) {
+            kq2 = __ffma2_rn(kr[r], qr[r], kq2);
 #pragma unroll
             for (int c = 0; c < CPT; ++c) {
               S[2 * i4 + r][c] = __fmul2_rn(dr[r], S[2 * i4 + r][c]);
               d2[c] = __ffma2_rn(S[2 * i4 + r][c], kr[r], d2[c]);
+              o2[c] = __ffma2_rn(S[2 * i4 + r][c], qr[r], o2[c]);
             }
           }
         }
         const float beta = dts[j];
+        float kqs = kq2.x + kq2.y;
+#pragma unroll
+        for (int off = PVW; off < 32; off <<= 1) kqs += __shfl_xor_sync(0xffffffffu, kqs, off);
 #pragma unroll
         for (int c = 0; c < CPT; ++c) {
-          float d = d2[c].x + d2[c].y;
+          float d = d2[c].x + d2[c].y, e = o2[c].x + o2[c].y;
 #pragma unroll
-          for (int off = PVW; off < 32; off <<= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
+          for (int off = PVW; off < 32; off <<= 1) {
+            d += __shfl_xor_sync(0xffffffffu, d, off);
+            e += __shfl_xor_sync(0xffffffffu, e, off);
+          }
           const float u = beta * (v_raw[c] - d);
           vv[c] = make_float2(u, u);
+          o[c] = fmaf(kqs, u, e);
+          if (kk == 0 && col + c < Dv)
+            p.out[(size_t)(tok0 + c0 + j) * p.out_stride + (size_t)h * Dv + col + c] = fmaf(head_skip, v_raw[c], o[c] * p.q_scale);
         }
 #pragma unroll
         for (int i4 = 0; i4 < NPT / 4; ++i4) {
-          const float4 kq = k4[i4], qq = q4[i4];
+          const float4 kq = k4[i4];
           const float2 kr[2] = {make_float2(kq.x, kq.y), make_float2(kq.z, kq.w)};
-          const float2 qr[2] = {make_float2(qq.x, qq.y), make_float2(qq.z, qq.w)};
 #pragma unroll
           for (int r = 0; r < 2; ++r) {
 #pragma unroll
-            for (int c = 0; c < CPT; ++c) {
-              S[2 * i4 + r][c] = __ffma2_rn(kr[r], vv[c], S[2 * i4 + r][c]);
-              o2[c] = __ffma2_rn(S[2 * i4 + r][c], qr[r], o2[c]);
-            }
+            for (int c = 0; c < CPT; ++c) S[2 * i4 + r][c] = __ffma2_rn(kr[r], vv[c], S[2 * i4 + r][c]);
           }
         }
       } else {
@@ -347,6 +364,7 @@ __global__ void __launch_bounds__(256) linear_scan_kernel(ScanParams p) {
         }
       }
       }
+      if constexpr (!DELTA) {                                // (the delta rule has stored its outputs above)
 #pragma unroll
       for (int c = 0; c < CPT; ++c) {
         o[c] = o2[c].x + o2[c].y;
@@ -354,6 +372,7 @@ __global__ void __launch_bounds__(256) linear_scan_kernel(ScanParams p) {
         for (int off = PVW; off < 32; off <<= 1) o[c] += __shfl_xor_sync(0xffffffffu, o[c], off);
         if (kk == 0 && col + c < Dv)
           p.out[(size_t)(tok0 + c0 + j) * p.out_stride + (size_t)h * Dv + col + c] = fmaf(head_skip, v_raw[c], o[c] * p.q_scale);
+      }
       }
     }
     __syncthreads();                                         // the buffer may be copied into again

@@ -31,7 +31,7 @@ from ..csrc import lib as K
 from ..phases import active as phases_active, phase
 from ..weights.store import TensorReq
 from .base import FeedForward, register_feed_forward
-from .linear import MODE_ADD, MODE_GEGLU, MODE_STORE, MODE_SWIGLU, project
+from .linear import MODE_ADD, MODE_CLAMPED_GLU, MODE_GEGLU, MODE_STORE, MODE_SWIGLU, project
 
 
 def _stack(a, b):
@@ -91,16 +91,13 @@ class DenseSwiGLU(FeedForward):
         with phase("mlp"):
             scale = None
             if self.w_token_gate is not None:
-                # one number per token, sigmoid(w . h) in float32: the router's kernels with a single expert
+                # one number per token, sigmoid(w . h) in float32: the router's dot-product kernel with a single row
                 scale = self.ws.get("ffn_token_gate", (T, 1), torch.float32)
-                K.router_topk(h, self.w_token_gate, self.ws.get("ffn_token_gate_idx", (T, 1), torch.int32), scale,
-                              top_k=1, sigmoid_gate=True, logits_out=self.ws.get("ffn_token_gate_z", (T, 1), torch.float32))
+                K.row_gates(h, self.w_token_gate, scale)
+            # the gate's activation (its clamps too) and the product with `up` happen in the epilogue of the first product
             if self.activation == "swish_clamped":
-                gu = self.ws.get("ffn_gate_up", (T, 2 * self.inter), torch.float32)
-                project(h, self.w_gate_up, gu)
-                K.gated_act(gu, a, self.activation, self.limit)
+                project(h, self.w_gate_up, a, MODE_CLAMPED_GLU, gate_limit=self.limit)
             else:
-                # the gate's activation and the product with `up` happen in the epilogue of the first product
                 project(h, self.w_gate_up, a, MODE_SWIGLU if self.activation == "silu" else MODE_GEGLU)
             project(a, self.w_down, residual, MODE_ADD if add else MODE_STORE, row_scale=scale)
 

@@ -190,6 +190,27 @@ def test_unit_vectors_sigmoid_gated_norm_branch_sum_concat_and_clamped_gate_kern
     assert (act.cpu().double() - gg * torch.sigmoid(1.702 * gg) * (uu + 1)).abs().max() < 1e-5
 
 
+@pytest.mark.parametrize("T,I,H,dtype", [(5, 72, 40, torch.float32), (40, 200, 136, torch.bfloat16),
+                                         (600, 256, 128, torch.bfloat16), (7, 96, 64, torch.bfloat16)])
+def test_clamped_gate_in_the_product_epilogue(T, I, H, dtype):
+    """out = g sigmoid(1.702 g) (u + 1), g = min(h Wg^T, limit), u = clamp(h Wu^T, -limit, limit), from one product
+    over [Wg; Wu]: on the float32 pipe, on the tensor-core kernel and on the paired kernel (many tokens, features a
+    multiple of 256); pre-activations a few limits wide, so that every clamp bites; also for experts in groups."""
+    from cpi_b200.parts.linear import MODE_CLAMPED_GLU, project
+    g = torch.Generator().manual_seed(T)
+    limit = 1.25
+    h = torch.randn(T, H, generator=g).to(dtype).cuda()
+    w = (torch.randn(2 * I, H, generator=g) * H ** -0.5 * 3).to(torch.bfloat16).cuda()
+    out = torch.empty(T, I, dtype=dtype, device="cuda")
+    project(h, w, out, MODE_CLAMPED_GLU, gate_limit=limit)
+    gu = h.double().cpu() @ w.double().cpu().T
+    gg, uu = gu[:, :I].clamp(max=limit), gu[:, I:].clamp(-limit, limit)
+    ref = gg * torch.sigmoid(1.702 * gg) * (uu + 1)
+    assert (gu[:, :I] > limit).any() and (gu[:, I:] < -limit).any()
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    assert (out.double().cpu() - ref).abs().max() < tol * ref.abs().max()
+
+
 @pytest.mark.parametrize("T", [5, 300])
 def test_router_with_a_bias_and_softmax_over_the_chosen(T):
     g = torch.Generator().manual_seed(T)
@@ -206,6 +227,9 @@ def test_router_with_a_bias_and_softmax_over_the_chosen(T):
         assert idx[t].tolist() == order
         assert (gate[t].cpu().double() - torch.softmax(z[t, order], 0)).abs().max() < 1e-5
     assert abs(gate.sum().item() - T) < 1e-3
+    gates = torch.empty(T, E, device=dev)
+    K().row_gates(h.to(dev), w.to(dev), gates, bias=b.to(dev))           # a gate per token and row, one launch
+    assert (gates.cpu().double() - torch.sigmoid(z)).abs().max() < 1e-5
 
 
 def test_kept_first_positions_in_the_attention_kernel():
