@@ -84,6 +84,37 @@ MIXED_C = model([
 ], width=40, vocab=64, loop=(0, 2, 3), mult=0.4)
 
 
+def draw_config(seed: int) -> dict:
+    """A configuration whose every size, option and constant is drawn from the seed: head counts and groups, head
+    sizes from 4 to 128 (keys, values and rotated parts of different sizes or equal), windows from 1 position to none,
+    kept first tokens from none to more than the window, taps 1 to 8, every kind of feed-forward, a loop anywhere."""
+    import random
+    rng = random.Random(seed)
+    n_layers = rng.randint(1, 4)
+    layers = []
+    for _ in range(n_layers):
+        G = rng.choice([1, 2, 3])
+        H = G * rng.choice([1, 2, 4])
+        D = rng.choice([8, 16, 20, 32, 64, 128])
+        Dv = rng.choice([D, D, 8, 24, 64])
+        l = left(H, G, D, Dv, window=rng.choice([None, 1, 7, 30, 64, 100]), keep_first=rng.choice([None, 0, 1, 20, 64, 70]),
+                 rot_dims=rng.choice([None, D, max(2, D // 4 * 2)]), base=rng.choice([100.0, 1e4, 5e5]),
+                 factor=rng.choice([None, 1.0, 2.0, 8.0]), scale=rng.choice([None, 2.0 / D ** 0.5]))
+        Gr = rng.choice([1, 2, 4])
+        Hr = Gr * rng.choice([1, 2, 3])
+        r = right(Hr, Gr, rng.choice([4, 10, 16, 32, 64, 128]), rng.choice([8, 13, 64, 128]), rng.choice([1, 2, 3, 4, 8]))
+        mlp = rng.choice([None, dense(rng.choice([24, 64, 256]), rng.choice([0.5, 2.0, 7.0])),
+                          moe(rng.choice([16, 96]), rng.choice([2, 12, 33]), 1, shared_ff=rng.choice([None, 32])),
+                          moe(rng.choice([16, 40]), 8, rng.choice([2, 4, 8]), shared_ff=rng.choice([None, 128]))])
+        layers.append(layer(l, r, mlp))
+    loop = None
+    if rng.random() < 0.6:
+        a = rng.randint(0, n_layers - 1)
+        loop = (a, rng.randint(a + 1, n_layers), rng.randint(1, 3))
+    return model(layers, width=rng.choice([24, 40, 64, 128, 264]), vocab=rng.choice([50, 131, 449]), loop=loop,
+                 eps=rng.choice([1e-5, 1e-6]), mult=rng.choice([None, 1.0, 0.5, 0.25]))
+
+
 def draw_weights(cfg: dict, seed: int, ranks=(6, 5)) -> dict:
     """{name: bfloat16 tensor} for a configuration; `ranks`: of the decay and the gate projection."""
     g = torch.Generator().manual_seed(seed)

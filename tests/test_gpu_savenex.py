@@ -119,7 +119,7 @@ class FakeBatch:
 
 # ---- kernels alone ---------------------------------------------------------------------------------------
 @pytest.mark.parametrize("rows,cols,heads,per_group", [(12, 20, 6, 2), (32, 64, 4, 1), (4, 20, 5, 1), (48, 24, 2, 2),
-                                                       (128, 128, 2, 1), (64, 96, 3, 3)])
+                                                       (128, 128, 2, 1), (64, 96, 3, 3), (10, 13, 2, 1), (200, 40, 2, 2)])
 def test_delta_rule_recurrence_whole_in_pieces_and_token_by_token(rows, cols, heads, per_group):
     """The delta rule with a decay per key channel, against the token loop of the plain implementation: a prompt in
     one launch (prepared decays and decays made in the kernel), in pieces of several sizes down to one token, in a
@@ -495,6 +495,28 @@ def test_other_constants_change_the_result_as_the_plain_implementation_says(tmp_
     for key in ("mult", "eps", "no_loop", "loop_all", "factor", "no_rot", "scale", "no_mask", "limit", "top", "no_shared",
                 "no_mlp", "conv"):
         assert (seen[key] - seen["base"]).abs().max() > 1e-3, key
+
+
+@pytest.mark.parametrize("seed", [1, 2, 3, 4, 5, 6, 7, 8])
+def test_configurations_drawn_from_a_seed(seed, tmp_path):
+    """Every size, option and constant drawn from a seed: a prompt with logits everywhere, a second request in a
+    portion and then both decoded together, in float32 to rounding and in bfloat16."""
+    import random
+    cfg = V.draw_config(seed)
+    rng = random.Random(seed)
+    b = Built(cfg, 40 + seed, tmp_path, ranks=(rng.choice([1, 5, 24]), rng.choice([2, 8, 17])))
+    vocab = cfg["vocab"]
+    ta, tb = V.tokens(110, vocab, seed), V.tokens(75, vocab, seed + 100)
+    for dtype in ("float32", "bfloat16"):
+        r = Run(b.engine(dtype, max_tokens=1024, max_seqs=2))
+        r.step([("a", ta[:90], range(90)), ("b", tb[:3], range(3))])
+        r.step([("b", tb[3:70], range(67))])
+        for i in range(5):
+            r.step([("a", ta[90 + i:91 + i], [0]), ("b", tb[70 + i:71 + i], [0])])
+        r.end("b")
+        for i in range(95, 110):
+            r.step([("a", ta[i:i + 1], [0])])
+        r.check(b, {"a": ta, "b": tb}, TOL[dtype])
 
 
 def test_layers_recorded_run_by_run(models):
