@@ -77,7 +77,8 @@ MIXED_B = model([
 ], width=128, vocab=384, eps=1e-6)
 
 # C: what the other two make equal or absent: a loop from the first layer that runs three times, a window of one,
-# no rotation, a convolution of one tap, more kept tokens than the window is wide, eight taps, a factor below one.
+# no rotation, a convolution of one tap, more kept tokens than the window is wide, eight taps, a factor below one, a
+# key size of four, one head, a single expert choice that takes every expert.
 MIXED_C = model([
     layer(left(2, 1, 16, 8, window=1, keep_first=2), right(2, 1, 16, 8, 1), dense(40, 0.5)),
     layer(left(1, 1, 40, 40, window=3, keep_first=7, rot_dims=40, factor=0.5), right(5, 5, 4, 20, 8), moe(24, 2, 2, shared_ff=8)),
