@@ -421,6 +421,23 @@ def test_unequal_batches_in_reused_slots(models, name, dtype):
     r.check(b, reqs, TOL[dtype])
 
 
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_steps_larger_than_the_engine_takes_run_as_pieces(models, name):
+    """An engine that takes 50 tokens a step gets steps of 191 and of 3 x 1 tokens: the first runs as pieces (whole
+    sequences, then runs of a long one) against the cache and state the pieces before left; same logits."""
+    b = models[name]
+    vocab = b.cfg["vocab"]
+    reqs = {"x": V.tokens(123, vocab, 80), "y": V.tokens(8, vocab, 81), "z": V.tokens(66, vocab, 82)}
+    for dtype in ("float32", "bfloat16"):
+        r = Run(b.engine(dtype, max_step_tokens=50, max_seqs=3, max_tokens=512))
+        r.step([("x", reqs["x"][:120], range(0, 120, 7)), ("y", reqs["y"][:7], [0, 6]), ("z", reqs["z"][:64], [1, 49, 50, 63])])
+        for k in range(1):
+            r.step([("x", reqs["x"][120:121], [0]), ("y", reqs["y"][7:8], [0]), ("z", reqs["z"][64:65], [0])])
+        r.end("y")
+        r.step([("x", reqs["x"][121:123], [0, 1]), ("z", reqs["z"][65:66], [0])])
+        r.check(b, reqs, TOL[dtype])
+
+
 def test_window_edges_and_kept_tokens_through_the_model(tmp_path):
     """One layer, one head, values that tell positions apart: moving the window or the kept count by one changes the
     logits as the plain implementation says, in a prompt and token by token, with the edge on a page border."""
