@@ -438,6 +438,23 @@ def test_steps_larger_than_the_engine_takes_run_as_pieces(models, name):
         r.check(b, reqs, TOL[dtype])
 
 
+def test_heads_of_128_through_the_model(tmp_path):
+    """Head size 128 on both sides (the 16-byte-per-lane preparation kernel, both tensor-core attention kernels with
+    kept tokens that end inside a key tile and beyond one, a 256-row state): a prompt of 380 tokens and 40 decoded."""
+    cfg = V.model([V.layer(V.left(4, 2, 128, 128, window=100, keep_first=70, rot_dims=128, factor=2.0), V.right(4, 2, 64, 128, 4), V.dense(512, 3.0)),
+                   V.layer(V.left(8, 1, 128, 128, window=200, keep_first=130, rot_dims=128), V.right(2, 2, 128, 128, 3), V.moe(128, 8, 2, shared_ff=128)),
+                   V.layer(V.left(2, 2, 128, 128, rot_dims=64), V.right(2, 1, 256, 64, 2), None)],
+                  width=256, vocab=500, loop=(0, 2, 2), mult=0.5)
+    b = Built(cfg, 77, tmp_path, ranks=(24, 24))
+    toks = V.tokens(420, 500, 3)
+    for dtype in ("float32", "bfloat16"):
+        r = Run(b.engine(dtype, max_tokens=2048, max_seqs=2))
+        r.step([("a", toks[:380], range(380))])
+        for i in range(380, 420):
+            r.step([("a", toks[i:i + 1], [0])])
+        r.check(b, {"a": toks}, TOL[dtype])
+
+
 def test_window_edges_and_kept_tokens_through_the_model(tmp_path):
     """One layer, one head, values that tell positions apart: moving the window or the kept count by one changes the
     logits as the plain implementation says, in a prompt and token by token, with the edge on a page border."""
